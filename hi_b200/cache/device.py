@@ -78,7 +78,7 @@ def pool_tokens_for_budget(cache_specs: Dict[int, Optional[CacheSpec]], element_
 
 class DeviceCache:
     def __init__(self, cache_specs: Dict[int, Optional[CacheSpec]], pages_per_group: Sequence[int], page_size: int,
-                 max_requests: int, dtype: torch.dtype, device):
+                 max_requests: int, dtype: torch.dtype, device, block_state_sizes: Optional[Dict[int, int]] = None):
         self.groups, self.group_of = plan_groups(cache_specs)
         self.page_size, self.dtype, self.device = page_size, dtype, torch.device(device)
         self.views: Dict[int, CacheView] = {}
@@ -98,13 +98,23 @@ class DeviceCache:
                 sdt = getattr(torch, spec.state_dtype)
                 view.state = torch.zeros((max_requests, *spec.state_shape), dtype=sdt, device=self.device)
                 self.bytes += view.state.numel() * view.state.element_size()
+            size = (block_state_sizes or {}).get(slot, 0)
+            if size:
+                view.block_state = torch.zeros((max_requests, size), dtype=torch.float32, device=self.device)
+                self.bytes += view.block_state.numel() * 4
             self.views[slot] = view
+
+    def state_tensors(self) -> List[torch.Tensor]:
+        """Every tensor of fixed-size per-request state (the mixers' and the block arrangements')."""
+        out = []
+        for view in self.views.values():
+            out += [t for t in (view.state, view.block_state) if t is not None]
+        return out
 
     def reset_slot(self, slot: int) -> None:
         """A request's fixed-size state starts at zero."""
-        for view in self.views.values():
-            if view.state is not None:
-                view.state[slot].zero_()
+        for t in self.state_tensors():
+            t[slot].zero_()
 
     def poison_pages(self, returned) -> None:
         """Debug aid: fill returned pages with NaN so a read of a freed page shows."""

@@ -91,7 +91,10 @@ def cmd_inspect(args) -> int:
         "kv_bytes_per_token_bf16": sum(2 * (2 if cs.values else 1) * cs.kv_heads * cs.head_dim
                                        for cs in model.cache_specs.values() if cs),
         "state_bytes_per_request": sum(4 * int(torch.Size(cs.state_shape).numel())
-                                       for cs in model.cache_specs.values() if cs and cs.state_shape),
+                                       for cs in model.cache_specs.values() if cs and cs.state_shape)
+                                   + 4 * sum(model.block_state_sizes.values()),
+        "interludes": [{"before_run": i, "part": spec.interludes[e.interlude].kind, "arg": e.interlude_arg}
+                       for i, e in enumerate(spec.schedule) if e.interlude is not None],
         "config": {k: v for k, v in vars(cfg).items() if k != "raw"},
     }
     try:

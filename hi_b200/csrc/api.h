@@ -13,7 +13,8 @@ int hb_embed_gather(const void* table, int table_dtype, const int* tokens, float
                     int vocab, float scale, cudaStream_t stream);
 // routed_weight (or null): [n * top_k] factors of the routed rows in the sum (a score that scales the
 // experts' outputs). The sum takes x_scale * x; post != 0: the stream takes the normalised row, not the sum.
-int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* routed, const int* slot_of_entry,
+int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* delta2, int delta2_dtype,
+                   const float* routed, const int* slot_of_entry,
                    const float* routed_weight, int top_k, const void* w, int w_dtype, void* y, int y_dtype, float* y_f32, const int* row_map,
                    int rows, int hidden, float eps, float x_scale, int post, cudaStream_t stream);
 int hb_swiglu(const void* in, void* out, int dtype, int rows, int inter, cudaStream_t stream);
@@ -29,7 +30,8 @@ int hb_moe_combine(const float* y, const int* slot_of_entry, const float* routed
 // norm after it), and a factor on cos and sin; what the lane-per-16-dims kernel cannot take runs in a general one
 int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, int rot_pairs, int interleaved, int qk_norm,
                 float qk_eps, int temp_on, float floor_scale, float attn_scale, const float* q_norm_w,
-                const float* k_norm_w, int norm_first, int norm_dim, float rot_mul, const int* positions,
+                const float* k_norm_w, int norm_first, int norm_dim, float rot_mul, const float* v_inv_freq,
+                int v_pairs, int v_interleaved, const int* positions,
                 const int* seq_of_token, const int* block_table, int table_stride, void* q_out, void* k_pages,
                 void* v_pages, int page_size, int write_kv, int n_tokens, int nh, int nkv, int hd,
                 cudaStream_t stream);
@@ -128,7 +130,13 @@ int hb_xielu(const void* in, void* out, int dtype, const float* coef, long long 
 // latent.cu: RMS-normed latent rows into their pages; a sigmoid gate per (token, head)
 int hb_latent_append(const void* in, int dtype, long long in_stride, const void* w, float eps, const int* positions,
                      const int* seq_of_token, const int* block_table, int table_stride, void* pages, int page_size,
-                     int rank, int row_len, int n_tokens, cudaStream_t stream);
+                     int rank, int row_len, int n_tokens, const float* inv_freq, int rot_pairs, int interleaved,
+                     cudaStream_t stream);
+int hb_rope_copy(const void* src, long long src_row, long long src_head, void* dst, long long dst_row,
+                 long long dst_head, int dtype, const int* positions, const float* inv_freq, int n_tokens, int heads,
+                 int pairs, int interleaved, cudaStream_t stream);
+int hb_rmsnorm_rows(const void* in, int dtype, long long in_stride, const void* w, float eps, void* out, int n_rows,
+                    int width, cudaStream_t stream);
 int hb_head_gate(const void* in, const void* gate, long long gate_stride, void* out, int dtype, int n_tokens,
                  int heads, int dim, cudaStream_t stream);
 
@@ -137,16 +145,19 @@ int hb_delta_prep(const void* proj, int proj_dtype, long long ld, int chan_off, 
                   float* state, long long state_stride, long long conv_off, const void* a_pre, int a_dtype,
                   const float* dt_bias, const float* a_log, const int* cu_seqlens, const int* seq_of_token,
                   const int* slots, float* q, float* k, float* v, float* beta, float* decay, int n_tokens, int heads,
-                  int kvh, int dim, int vdim, int taps_n, cudaStream_t stream);
+                  int kvh, int dim, int vdim, int taps_n, int head_decay, cudaStream_t stream);
+int hb_gla_prep(const void* proj, int proj_dtype, long long ld, int q_off, int k_off, int v_off, const float* z,
+                const float* bias, float tau, float q_scale, float* q, float* k, float* v, float* decay, int n_tokens,
+                int qk_cols, int v_cols, cudaStream_t stream);
 int hb_delta_conv_update(const void* proj, int proj_dtype, long long ld, int chan_off, float* state,
                          long long state_stride, long long conv_off, const int* cu_seqlens, const int* slots,
                          int n_seqs, int channels, int taps_n, cudaStream_t stream);
 int hb_delta_recurrence(const float* q, const float* k, const float* v, const float* beta, const float* decay,
                         float* state, long long state_stride, const int* cu_seqlens, const int* slots, float* out,
-                        int n_seqs, int heads, int kvh, int dim, int vdim, int variant, int single_tokens,
+                        int n_seqs, int heads, int kvh, int dim, int vdim, int variant, int single_tokens, int plain,
                         cudaStream_t stream);   // variant: 0 chosen by sizes, 1 S in shared memory, 16 / 32 rows a lane
 int hb_delta_out_norm(const float* o, const void* gate, int gate_dtype, const void* w, float eps, void* out, int dtype,
-                      long long rows, int vdim, cudaStream_t stream);
+                      long long rows, int vdim, int gate_silu, long long gate_stride, int heads, cudaStream_t stream);
 
 // mlstm.cu: the matrix memory of the mLSTM (gates and running maximum; S and n token after token; output norm).
 // A request's state row: [heads][vdim + 1][dim] float32 (S column by column, then n), then m [heads] at m_off.
@@ -164,6 +175,24 @@ int hb_mlstm_out_norm(const float* o, const float* nq, const float* floor_, cons
 // seeded random weights: out[i] = value of element first + i of the tensor with `key` (random_fill.cu)
 int hb_random_normal(void* out, int dtype, long long n, long long first, unsigned long long key, float scale,
                      cudaStream_t stream);
+
+// canon.cu: the norm's output through a short causal convolution over time per channel, kept float32 between the
+// two; what is added to the stream between passes over a range of layers; the mean of two normed mixer outputs
+int hb_canon_conv(const float* h, const float* taps_a, const float* taps_b, float* state, long long state_stride,
+                  const int* cu_seqlens, const int* seq_of_token, const int* slots, void* out_a, void* out_b, int dtype,
+                  int n_tokens, int n_seqs, int width, int taps_n, int update_state, cudaStream_t stream);
+int hb_stream_add(float* x, const void* d1, int d1_dtype, const void* d2, int d2_dtype, const float* e,
+                  const float* vec, long long rows, int width, cudaStream_t stream);
+int hb_rmsnorm_mean2(const void* a, const void* b, int in_dtype, const void* wa, const void* wb, int w_dtype, float eps,
+                     void* out, int out_dtype, int rows, int width, cudaStream_t stream);
+
+// sigmoid_attention.cu: weights sigmoid(score + bias[head]), not normalised; values cached rotated and the sum
+// turned back (v_inv_freq null: values as they are)
+int hb_sigmoid_attention(const void* q, int dtype, const void* k_pages, const void* v_pages, const int* block_table,
+                         int table_stride, const int* seq_of_token, const int* positions, const float* head_bias,
+                         const float* v_inv_freq, int v_pairs, int v_interleaved, void* out, int n_tokens, int nh,
+                         int nkv, int hd, int page_size, int chunk, int window, float scale, int split_size,
+                         int max_splits, float* part_acc, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -10,7 +10,9 @@
 //                        S <- decay * S (rows);  u = beta * (v - S^T k);  S <- S + k u^T;  o = S^T q
 //                      A thread owns one column of S, so nothing is exchanged between threads but k, q and the
 //                      decay of the token, which the block stages in shared memory one token ahead.
-//   delta_out_norm     o / sqrt(mean_vdim(o^2) + eps) * w * sigmoid(gate)
+//   delta_out_norm     o / sqrt(mean_vdim(o^2) + eps) * w * sigmoid(gate)   (or * silu(gate))
+//   gla_prep           the inputs of the same recurrence without the correction (S <- decay * S + k v^T):
+//                      q * dim^-1/2, k, v as float32 and decay = sigmoid(z + b)^(1 / tau) per key channel
 //
 // Everything here is float32 arithmetic; only the projections that come in and the normed output that
 // goes out have the engine's dtype. The state of a request depends on its own tokens only and the order of
@@ -34,9 +36,10 @@ struct PrepArgs {
   const float* taps;         // [C, K]
   float* state;              // [slots, state_stride]
   long long state_stride, conv_off;
-  const void* a_pre;         // [N, heads * dim]
+  const void* a_pre;         // [N, heads * dim]; with head_decay [N, heads]: one decay per head
   int a_dtype;
-  const float* dt_bias;      // [heads * dim]
+  int head_decay;
+  const float* dt_bias;      // [heads * dim] ([heads] with head_decay)
   const float* a_log;        // [heads]
   const int* cu_seqlens;
   const int* seq_of_token;
@@ -88,6 +91,13 @@ __global__ void delta_prep_kernel(const PrepArgs a, int longest) {
       if (lane == 0)
         a.beta[(size_t)t * a.heads + h] = sigmoid1(ldf(a.proj, a.proj_dtype, (size_t)t * a.ld + a.beta_off + h));
       const float rate = expf(a.a_log[h]);
+      if (a.head_decay) {
+        // one decay for all key channels of the head, written out per channel: the recurrence reads rows of decays
+        const float x = ldf(a.a_pre, a.a_dtype, (size_t)t * a.heads + h) + a.dt_bias[h];
+        const float sp = x > 20.f ? x : log1pf(expf(x));
+        const float g = expf(-rate * sp);
+        for (int i = lane; i < a.dim; i += 32) a.decay[(size_t)t * a.heads * a.dim + (size_t)h * a.dim + i] = g;
+      } else
       for (int i = lane; i < a.dim; i += 32) {
         const size_t at = (size_t)t * a.heads * a.dim + (size_t)h * a.dim + i;
         const float x = ldf(a.a_pre, a.a_dtype, at) + a.dt_bias[(size_t)h * a.dim + i];
@@ -133,6 +143,7 @@ struct RecurArgs {
   const int* slots;
   float* out;           // [N, heads * vdim]
   int heads, kvh, dim, vdim;
+  int plain;            // 1: no correction, S <- decay * S + k v^T (beta is not read)
 };
 
 // Stage token t's k, q and decay rows (dim floats each) into buf[0..3*DIMP): k, q, g.
@@ -235,8 +246,9 @@ __global__ void __launch_bounds__(kRecurThreads) delta_recurrence_reg_kernel(con
         cp_async4(dst + tok * TOK + 3 * DIMP + c, a.v + (size_t)(t0 + tok) * v_row + (size_t)head * a.vdim + col0 + c);
       }
     }
-    for (int tok = threadIdx.x; tok < cnt; tok += kRecurThreads)
-      cp_async4(dst + tok * TOK + 3 * DIMP + BCOLS, a.beta + (size_t)(t0 + tok) * a.heads + head);
+    if (!a.plain)
+      for (int tok = threadIdx.x; tok < cnt; tok += kRecurThreads)
+        cp_async4(dst + tok * TOK + 3 * DIMP + BCOLS, a.beta + (size_t)(t0 + tok) * a.heads + head);
   };
   stage(first, 0);
   cp_async_commit();
@@ -283,7 +295,7 @@ __global__ void __launch_bounds__(kRecurThreads) delta_recurrence_reg_kernel(con
         sq += __shfl_xor_sync(0xffffffffu, sq, o);
         kq += __shfl_xor_sync(0xffffffffu, kq, o);
       }
-      const float u = bt * (vj - dot);
+      const float u = a.plain ? vj : bt * (vj - dot);
       const float out = fmaf(u, kq, sq);
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) s[r] = fmaf(kk[r], u, s[r]);
@@ -335,14 +347,14 @@ __global__ void delta_recurrence_smem_kernel(const RecurArgs a) {
     const float* cur = stage0 + (size_t)((t - first) & 1) * 3 * dim;
     if (t + 1 < last) stage_token(a, t + 1, head, kvhead, stage0 + (size_t)((t - first + 1) & 1) * 3 * dim, dim);
     const float vj = active ? a.v[(size_t)t * a.heads * a.vdim + (size_t)head * a.vdim + col] : 0.f;
-    const float bt = a.beta[(size_t)t * a.heads + head];
+    const float bt = a.plain ? 1.f : a.beta[(size_t)t * a.heads + head];
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int i = 0; i < dim; ++i) {
       const float si = mine[(size_t)i * cols] * cur[2 * dim + i];
       mine[(size_t)i * cols] = si;
       acc[i & 3] = fmaf(si, cur[i], acc[i & 3]);
     }
-    const float u = bt * (vj - ((acc[0] + acc[1]) + (acc[2] + acc[3])));
+    const float u = a.plain ? vj : bt * (vj - ((acc[0] + acc[1]) + (acc[2] + acc[3])));
     float o[4] = {0.f, 0.f, 0.f, 0.f};
     for (int i = 0; i < dim; ++i) {
       const float si = fmaf(cur[i], u, mine[(size_t)i * cols]);
@@ -360,7 +372,7 @@ __global__ void delta_recurrence_smem_kernel(const RecurArgs a) {
 template <typename T>
 __global__ void delta_out_norm_kernel(const float* __restrict__ o, const void* __restrict__ gate, int gate_dtype,
                                       const T* __restrict__ w, float eps, T* __restrict__ out, long long rows,
-                                      int vdim) {
+                                      int vdim, int gate_silu, long long gate_stride, int heads) {
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -369,19 +381,48 @@ __global__ void delta_out_norm_kernel(const float* __restrict__ o, const void* _
   for (int j = lane; j < vdim; j += 32) ss += src[j] * src[j];
   const float inv = 1.f / sqrtf(hb::warp_sum(ss) / (float)vdim + eps);
   for (int j = lane; j < vdim; j += 32) {
-    const float g = sigmoid1(ldf(gate, gate_dtype, (size_t)row * vdim + j));
+    const float gx = ldf(gate, gate_dtype, (size_t)(row / heads) * gate_stride + (size_t)(row % heads) * vdim + j);
+    const float g = gate_silu ? gx * sigmoid1(gx) : sigmoid1(gx);
     out[row * vdim + j] = hb::from_f32<T>(src[j] * inv * hb::to_f32(w[j]) * g);
   }
 }
 
+// q, k [N, heads * dim], v [N, heads * vdim] from columns of proj; decay = exp(-softplus(-(z + b)) / tau).
+__global__ void gla_prep_kernel(const void* __restrict__ proj, int proj_dtype, long long ld, int q_off, int k_off,
+                                int v_off, const float* __restrict__ z, const float* __restrict__ bias, float inv_tau,
+                                float q_scale, float* __restrict__ q, float* __restrict__ k, float* __restrict__ v,
+                                float* __restrict__ decay, int qk_cols, int v_cols) {
+  const size_t t = blockIdx.x;
+  for (int c = threadIdx.x; c < qk_cols; c += blockDim.x) {
+    q[t * qk_cols + c] = ldf(proj, proj_dtype, t * ld + q_off + c) * q_scale;
+    k[t * qk_cols + c] = ldf(proj, proj_dtype, t * ld + k_off + c);
+    const float x = -(z[t * qk_cols + c] + (bias ? bias[c] : 0.f));
+    const float sp = x > 20.f ? x : log1pf(expf(x));        // -log sigmoid(z + b)
+    decay[t * qk_cols + c] = expf(-sp * inv_tau);
+  }
+  for (int c = threadIdx.x; c < v_cols; c += blockDim.x) v[t * v_cols + c] = ldf(proj, proj_dtype, t * ld + v_off + c);
+}
+
 }  // namespace
+
+extern "C" int hb_gla_prep(const void* proj, int proj_dtype, long long ld, int q_off, int k_off, int v_off,
+                           const float* z, const float* bias, float tau, float q_scale, float* q, float* k, float* v,
+                           float* decay, int n_tokens, int qk_cols, int v_cols, cudaStream_t stream) {
+  if (!proj || !z || !q || !k || !v || !decay || n_tokens < 0 || qk_cols <= 0 || v_cols <= 0 || !(tau > 0.f))
+    return HB_ERR_BAD_ARG;
+  if (n_tokens == 0) return HB_OK;
+  gla_prep_kernel<<<n_tokens, 256, 0, stream>>>(proj, proj_dtype, ld, q_off, k_off, v_off, z, bias, 1.f / tau, q_scale,
+                                                q, k, v, decay, qk_cols, v_cols);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
 
 extern "C" int hb_delta_prep(const void* proj, int proj_dtype, long long ld, int chan_off, int beta_off,
                              const float* taps, float* state, long long state_stride, long long conv_off,
                              const void* a_pre, int a_dtype, const float* dt_bias, const float* a_log,
                              const int* cu_seqlens, const int* seq_of_token, const int* slots, float* q, float* k,
                              float* v, float* beta, float* decay, int n_tokens, int heads, int kvh, int dim, int vdim,
-                             int taps_n, cudaStream_t stream) {
+                             int taps_n, int head_decay, cudaStream_t stream) {
   if (!proj || !taps || !state || !a_pre || !dt_bias || !a_log || !cu_seqlens || !seq_of_token || !slots || !q || !k ||
       !v || !beta || !decay)
     return HB_ERR_BAD_ARG;
@@ -394,6 +435,7 @@ extern "C" int hb_delta_prep(const void* proj, int proj_dtype, long long ld, int
   PrepArgs a;
   a.proj = proj; a.proj_dtype = proj_dtype; a.ld = ld; a.chan_off = chan_off; a.beta_off = beta_off; a.taps = taps;
   a.state = state; a.state_stride = state_stride; a.conv_off = conv_off; a.a_pre = a_pre; a.a_dtype = a_dtype;
+  a.head_decay = head_decay;
   a.dt_bias = dt_bias; a.a_log = a_log; a.cu_seqlens = cu_seqlens; a.seq_of_token = seq_of_token; a.slots = slots;
   a.q = q; a.k = k; a.v = v; a.beta = beta; a.decay = decay;
   a.heads = heads; a.kvh = kvh; a.dim = dim; a.vdim = vdim; a.K = taps_n;
@@ -421,13 +463,14 @@ extern "C" int hb_delta_conv_update(const void* proj, int proj_dtype, long long 
 extern "C" int hb_delta_recurrence(const float* q, const float* k, const float* v, const float* beta,
                                    const float* decay, float* state, long long state_stride, const int* cu_seqlens,
                                    const int* slots, float* out, int n_seqs, int heads, int kvh, int dim, int vdim,
-                                   int variant, int single_tokens, cudaStream_t stream) {
-  if (!q || !k || !v || !beta || !decay || !state || !cu_seqlens || !slots || !out) return HB_ERR_BAD_ARG;
+                                   int variant, int single_tokens, int plain, cudaStream_t stream) {
+  if (!q || !k || !v || (!beta && !plain) || !decay || !state || !cu_seqlens || !slots || !out) return HB_ERR_BAD_ARG;
   if (heads <= 0 || kvh <= 0 || heads % kvh || dim <= 0 || vdim <= 0 || n_seqs < 0) return HB_ERR_BAD_ARG;
   if (n_seqs == 0) return HB_OK;
   RecurArgs a;
   a.q = q; a.k = k; a.v = v; a.beta = beta; a.decay = decay; a.state = state; a.state_stride = state_stride;
   a.cu_seqlens = cu_seqlens; a.slots = slots; a.out = out; a.heads = heads; a.kvh = kvh; a.dim = dim; a.vdim = vdim;
+  a.plain = plain ? 1 : 0;
   if (variant != 1 && variant != 0 && variant != 16 && variant != 32) return HB_ERR_BAD_ARG;
   if (variant != 1 && dim <= 256) {
     // How many rows of a column a lane holds (`variant`, 0: chosen here). A step of single tokens is bound by
@@ -464,18 +507,21 @@ extern "C" int hb_delta_recurrence(const float* q, const float* k, const float* 
 }
 
 extern "C" int hb_delta_out_norm(const float* o, const void* gate, int gate_dtype, const void* w, float eps, void* out,
-                                 int dtype, long long rows, int vdim, cudaStream_t stream) {
-  if (!o || !gate || !w || !out || rows < 0 || vdim <= 0) return HB_ERR_BAD_ARG;
+                                 int dtype, long long rows, int vdim, int gate_silu, long long gate_stride, int heads,
+                                 cudaStream_t stream) {
+  if (!o || !gate || !w || !out || rows < 0 || vdim <= 0 || heads <= 0 || gate_stride < (long long)heads * vdim)
+    return HB_ERR_BAD_ARG;
   if (rows == 0) return HB_OK;
   const int warps = 4;
   const long long blocks = (rows + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return HB_ERR_UNSUPPORTED;
   if (dtype == HB_DTYPE_F32)
     delta_out_norm_kernel<float><<<(int)blocks, warps * 32, 0, stream>>>(o, gate, gate_dtype, (const float*)w, eps,
-                                                                         (float*)out, rows, vdim);
+                                                                         (float*)out, rows, vdim, gate_silu,
+                                                                         gate_stride, heads);
   else if (dtype == HB_DTYPE_BF16)
     delta_out_norm_kernel<__nv_bfloat16><<<(int)blocks, warps * 32, 0, stream>>>(
-        o, gate, gate_dtype, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)out, rows, vdim);
+        o, gate, gate_dtype, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)out, rows, vdim, gate_silu, gate_stride, heads);
   else
     return HB_ERR_BAD_ARG;
   HB_LAUNCH_CHECK();

@@ -52,11 +52,12 @@ __global__ void embed_gather_kernel(const void* table, int table_dtype, const in
 }
 
 // Row r of the output: src = row_map ? row_map[r] : r.
-//   s = x_scale * x[src] (+ delta[src]);  if no row_map: x[src] = s  (the residual sum, float32)
+//   s = x_scale * x[src] (+ delta[src]) (+ delta2[src]);  if no row_map: x[src] = s  (the residual sum, float32)
 //   y[r] = s * rsqrt(mean(s^2) + eps) * w     (crates/hi-cuda/src/kernels.cu:61-77)
 // post != 0 (a block whose norm comes after the sum): the stream takes the normalised row instead of
 // the sum, x[src] = y[r] unrounded.
-__global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype, const float* routed,
+__global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype, const void* delta2, int delta2_dtype,
+                                   const float* routed,
                                    const int* slot_of_entry, const float* routed_weight, int top_k, const void* w,
                                    int w_dtype, void* y, int y_dtype, float* y_f32, const int* row_map,
                                    int hidden, float eps, float x_scale, int post) {
@@ -68,6 +69,7 @@ __global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype,
   for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
     float s = x[src * hidden + j] * x_scale;
     if (delta) s += load_any(delta, delta_dtype, src * hidden + j);
+    if (delta2) s += load_any(delta2, delta2_dtype, src * hidden + j);
     if (routed)
       for (int q = 0; q < top_k; ++q)
         s += routed[(size_t)slot_of_entry[src * top_k + q] * hidden + j] * (routed_weight ? routed_weight[src * top_k + q] : 1.f);
@@ -79,7 +81,7 @@ __global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype,
   for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
     const float s = row[j];
     const float wv = w ? load_any(w, w_dtype, j) : 1.f;
-    if (!row_map && (delta || routed || post)) x[src * hidden + j] = post ? s * inv * wv : s;
+    if (!row_map && (delta || delta2 || routed || post)) x[src * hidden + j] = post ? s * inv * wv : s;
     store_any(y, y_dtype, (size_t)r * hidden + j, s * inv * wv);
     if (y_f32) y_f32[(size_t)r * hidden + j] = s * inv * wv;
   }
@@ -92,6 +94,7 @@ __global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype,
 // (the combine of crates/hi-cuda/src/kernels.cu:10661-10680, in rank order, fused into the norm).
 template <int NG>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __restrict__ delta, int delta_dtype,
+                                       const void* __restrict__ delta2, int delta2_dtype,
                                        const float* __restrict__ routed, const int* __restrict__ slot_of_entry,
                                        const float* __restrict__ routed_weight, int top_k, const void* __restrict__ w, int w_dtype, void* __restrict__ y,
                                        int y_dtype, float* __restrict__ y_f32, const int* __restrict__ row_map,
@@ -120,6 +123,10 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
         const float4 d = load4_any(delta, delta_dtype, src * hidden + idx);
         a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
       }
+      if (delta2) {
+        const float4 d = load4_any(delta2, delta2_dtype, src * hidden + idx);
+        a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+      }
       if (routed) {
         for (int j = 0; j < top_k; ++j) {
           const float4 d = *reinterpret_cast<const float4*>(routed + (size_t)slots[j] * hidden + idx);
@@ -138,7 +145,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
     if (idx < hidden) {
       const float4 a = v[g];
       const float4 o = make_float4(a.x * inv * wv[g].x, a.y * inv * wv[g].y, a.z * inv * wv[g].z, a.w * inv * wv[g].w);
-      if (!row_map && (delta || routed || post)) *reinterpret_cast<float4*>(x + src * hidden + idx) = post ? o : a;
+      if (!row_map && (delta || delta2 || routed || post)) *reinterpret_cast<float4*>(x + src * hidden + idx) = post ? o : a;
       store4_any(y, y_dtype, (size_t)r * hidden + idx, o);
       if (y_f32) *reinterpret_cast<float4*>(y_f32 + (size_t)r * hidden + idx) = o;
     }
@@ -202,11 +209,13 @@ extern "C" int hb_feed_tokens(int* tokens, const int* dst, const int* src, const
   return HB_OK;
 }
 
-extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* routed,
+extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* delta2, int delta2_dtype,
+                              const float* routed,
                               const int* slot_of_entry, const float* routed_weight, int top_k, const void* w, int w_dtype, void* y, int y_dtype,
                               float* y_f32, const int* row_map, int rows, int hidden, float eps,
                               float x_scale, int post, cudaStream_t stream) {
   if (!x || !y || rows < 0 || hidden <= 0 || !dtype_ok(y_dtype) || (delta && !dtype_ok(delta_dtype)) ||
+      (delta2 && !dtype_ok(delta2_dtype)) ||
       (w && !dtype_ok(w_dtype)))
     return HB_ERR_BAD_ARG;
   if (routed && (!slot_of_entry || top_k < 1 || top_k > 8)) return HB_ERR_BAD_ARG;
@@ -216,7 +225,7 @@ extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
     const int threads = groups >= 512 ? 512 : ((groups + 31) / 32) * 32;
     const int ng = (groups + threads - 1) / threads;
 #define HB_NORM_LAUNCH(NG)                                                                                   \
-    add_rmsnorm_vec_kernel<NG><<<rows, threads, 0, stream>>>(x, delta, delta_dtype, routed, slot_of_entry, routed_weight, top_k, \
+    add_rmsnorm_vec_kernel<NG><<<rows, threads, 0, stream>>>(x, delta, delta_dtype, delta2, delta2_dtype, routed, slot_of_entry, routed_weight, top_k, \
                                                              w, w_dtype, y, y_dtype, y_f32, row_map, hidden, eps, x_scale, post)
     if (ng <= 1) HB_NORM_LAUNCH(1);
     else if (ng <= 2) HB_NORM_LAUNCH(2);
@@ -233,7 +242,7 @@ extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
     if (e != cudaSuccess) return (int)e;
   }
   const int threads = hidden >= 2048 ? 512 : 256;
-  add_rmsnorm_kernel<<<rows, threads, smem, stream>>>(x, delta, delta_dtype, routed, slot_of_entry, routed_weight, top_k, w, w_dtype,
+  add_rmsnorm_kernel<<<rows, threads, smem, stream>>>(x, delta, delta_dtype, delta2, delta2_dtype, routed, slot_of_entry, routed_weight, top_k, w, w_dtype,
                                                       y, y_dtype, y_f32, row_map, hidden, eps, x_scale, post);
   HB_LAUNCH_CHECK();
   return HB_OK;

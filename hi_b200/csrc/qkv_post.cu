@@ -172,15 +172,18 @@ __global__ void qkv_post_general_kernel(const T* __restrict__ qkv, const float* 
                                         int interleaved, int qk_norm, float qk_eps, int temp_on, float floor_scale,
                                         float attn_scale, const float* __restrict__ q_w, const float* __restrict__ k_w,
                                         int norm_first, int norm_dim, float rot_mul,
+                                        const float* __restrict__ v_inv_freq, int v_pairs, int v_interleaved,
                                         const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                         const int* __restrict__ block_table, int table_stride, T* __restrict__ q_out,
                                         T* __restrict__ k_pages, T* __restrict__ v_pages, int page_size, int write_kv,
                                         int nh, int nkv, int hd) {
-  extern __shared__ float smem_g[];            // [rot_pairs] cos, [rot_pairs] sin, [warps][hd] rows
+  extern __shared__ float smem_g[];            // [rot_pairs] cos, sin, [v_pairs] cos, sin, [warps][hd] rows
   float* cs = smem_g;
   float* sn = cs + rot_pairs;
+  float* vcs = sn + rot_pairs;
+  float* vsn = vcs + v_pairs;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  float* row = sn + rot_pairs + warp * hd;
+  float* row = vsn + v_pairs + warp * hd;
   const int t = blockIdx.x;
   const int pos = positions[t];
   for (int j = threadIdx.x; j < rot_pairs; j += blockDim.x) {
@@ -189,6 +192,8 @@ __global__ void qkv_post_general_kernel(const T* __restrict__ qkv, const float* 
     cs[j] = c_ * rot_mul;
     sn[j] = s_ * rot_mul;
   }
+  if (write_kv)
+    for (int j = threadIdx.x; j < v_pairs; j += blockDim.x) sincosf((float)pos * v_inv_freq[j], &vsn[j], &vcs[j]);
   __syncthreads();
   const int heads_total = nh + 2 * nkv;
   const int rot = 2 * rot_pairs;
@@ -206,7 +211,27 @@ __global__ void qkv_post_general_kernel(const T* __restrict__ qkv, const float* 
     }
     const T* src = qkv + ((size_t)t * heads_total + head) * hd;
     if (kind == 2) {
-      for (int d = lane; d < hd; d += 32) dst[d] = src[d];
+      if (v_pairs == 0) {
+        for (int d = lane; d < hd; d += 32) dst[d] = src[d];
+        continue;
+      }
+      // values cached rotated by their own position: the first 2 * v_pairs dims, pair m by pos * v_inv_freq[m]
+      for (int d = lane; d < hd; d += 32) row[d] = hb::to_f32(src[d]);
+      __syncwarp();
+      for (int d = lane; d < hd; d += 32) {
+        float y = row[d];
+        if (d < 2 * v_pairs) {
+          if (v_interleaved) {
+            const int j = d >> 1;
+            y = (d & 1) ? row[d] * vcs[j] + row[d - 1] * vsn[j] : row[d] * vcs[j] - row[d + 1] * vsn[j];
+          } else {
+            y = d < v_pairs ? row[d] * vcs[d] - row[d + v_pairs] * vsn[d]
+                            : row[d] * vcs[d - v_pairs] + row[d - v_pairs] * vsn[d - v_pairs];
+          }
+        }
+        dst[d] = hb::from_f32<T>(y);
+      }
+      __syncwarp();
       continue;
     }
     const float* w = kind == 0 ? q_w : k_w;
@@ -250,6 +275,7 @@ __global__ void qkv_post_general_kernel(const T* __restrict__ qkv, const float* 
 extern "C" int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, int rot_pairs, int interleaved,
                            int qk_norm, float qk_eps, int temp_on, float floor_scale, float attn_scale,
                            const float* q_norm_w, const float* k_norm_w, int norm_first, int norm_dim, float rot_mul,
+                           const float* v_inv_freq, int v_pairs, int v_interleaved,
                            const int* positions, const int* seq_of_token, const int* block_table,
                            int table_stride, void* q_out, void* k_pages, void* v_pages, int page_size,
                            int write_kv, int n_tokens, int nh, int nkv, int hd, cudaStream_t stream) {
@@ -261,20 +287,23 @@ extern "C" int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, in
   if (temp_on && !(floor_scale > 0.f)) return HB_ERR_BAD_ARG;
   if (norm_dim <= 0) norm_dim = hd;
   if (norm_dim > hd || 2 * rot_pairs > norm_dim) return HB_ERR_BAD_ARG;
+  if (!v_inv_freq) v_pairs = 0;
+  if (v_pairs < 0 || 2 * v_pairs > hd) return HB_ERR_BAD_ARG;
   if (n_tokens == 0) return HB_OK;
-  const bool fast = hd % 16 == 0 && hd <= kMaxHeadDim && rot_pairs % 8 == 0 /* whole lanes rotate */ && norm_dim == hd &&
+  const bool fast = v_pairs == 0 && hd % 16 == 0 && hd <= kMaxHeadDim && rot_pairs % 8 == 0 /* whole lanes rotate */ && norm_dim == hd &&
                     (norm_first || (!q_norm_w && !k_norm_w && rot_mul == 1.f));
   if (!fast) {
     // a norm after a rotation that changes lengths would need the rotated squares; no model asks for it
     if (qk_norm && !norm_first && (rot_mul != 1.f || q_norm_w || k_norm_w)) return HB_ERR_UNSUPPORTED;
     const int heads_all = nh + 2 * nkv;
     const int warps = heads_all < 8 ? heads_all : 8;
-    const size_t smem = (size_t)(2 * rot_pairs + warps * hd) * sizeof(float);
+    const size_t smem = (size_t)(2 * rot_pairs + 2 * v_pairs + warps * hd) * sizeof(float);
     if (smem > 48 * 1024) return HB_ERR_UNSUPPORTED;
 #define HB_QKV_GENERAL(T)                                                                                          \
     qkv_post_general_kernel<T><<<n_tokens, warps * 32, smem, stream>>>(                                             \
         (const T*)qkv, inv_freq, rot_pairs, interleaved, qk_norm, qk_eps, temp_on, floor_scale, attn_scale, q_norm_w, \
-        k_norm_w, norm_first, norm_dim, rot_mul, positions, seq_of_token, block_table, table_stride, (T*)q_out,     \
+        k_norm_w, norm_first, norm_dim, rot_mul, v_inv_freq, v_pairs, v_interleaved, positions, seq_of_token,       \
+        block_table, table_stride, (T*)q_out,                                                                       \
         (T*)k_pages, (T*)v_pages, page_size, write_kv, nh, nkv, hd)
     if (dtype == HB_DTYPE_F32) HB_QKV_GENERAL(float);
     else if (dtype == HB_DTYPE_BF16) HB_QKV_GENERAL(__nv_bfloat16);

@@ -120,7 +120,7 @@ class Engine:
             pages.append(max(1, -(-int(tokens) // self.page_size)))
         self.manager = CacheManager(groups, pages, self.page_size, max_active_requests)
         self.cache = DeviceCache(model.cache_specs, pages, self.page_size, max_active_requests, model.dtype,
-                                 self.device)
+                                 self.device, block_state_sizes=model.block_state_sizes)
         self.vocab_size = model.spec.vocab_size
         self.stats = EngineStats()
         self.debug_poison = debug_poison
@@ -460,7 +460,7 @@ class _DecodeGraph:
         # The run outside the capture executes the step, and so does the first replay. Appending a token's
         # keys twice writes the same rows twice; advancing a recurrent mixer's state twice does not give
         # the same state, so the requests' fixed-size states are put back after the run.
-        states = [(view.state, view.state.clone()) for view in eng.cache.views.values() if view.state is not None]
+        states = [(t, t.clone()) for t in eng.cache.state_tensors()]
         stream = torch.cuda.Stream()
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):                                   # once outside capture, on a side stream

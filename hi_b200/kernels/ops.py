@@ -19,13 +19,13 @@ P, I, F = c_void_p, c_int, c_float
 _SIGNATURES = {
     "hb_feed_tokens": [P, P, P, P, I, P],
     "hb_embed_gather": [P, I, P, P, I, I, I, F, P],
-    "hb_add_rmsnorm": [P, P, I, P, P, P, I, P, I, P, I, P, P, I, I, F, F, I, P],
+    "hb_add_rmsnorm": [P, P, I, P, I, P, P, P, I, P, I, P, I, P, P, I, I, F, F, I, P],
     "hb_swiglu": [P, P, I, I, I, P],
     "hb_relu2": [P, I, P, I, c_longlong, P],
     "hb_softcap": [P, F, c_longlong, P],
     "hb_convert": [P, I, P, I, c_longlong, P],
     "hb_moe_combine": [P, P, P, P, I, P, I, I, I, P],
-    "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, I, I, F, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
+    "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, I, I, F, P, I, I, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
     "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P],
     "hb_attention_merge": [P, P, P, I, I, I, I, I, P],
     "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P],
@@ -49,13 +49,20 @@ _SIGNATURES = {
     "hb_random_normal": [P, I, c_longlong, c_longlong, c_uint64, F, P],
     "hb_gated_depth_dyt": [P, P, I, P, I, P, I, P, I, P, c_longlong, I, P, P, P, P, P, P, P, P, P, P, I, I, P, I, I, P],
     "hb_xielu": [P, P, I, P, c_longlong, P],
-    "hb_latent_append": [P, I, c_longlong, P, F, P, P, P, I, P, I, I, I, I, P],
+    "hb_latent_append": [P, I, c_longlong, P, F, P, P, P, I, P, I, I, I, I, P, I, I, P],
+    "hb_rmsnorm_rows": [P, I, c_longlong, P, F, P, I, I, P],
+    "hb_rope_copy": [P, c_longlong, c_longlong, P, c_longlong, c_longlong, I, P, P, I, I, I, I, P],
+    "hb_canon_conv": [P, P, P, P, c_longlong, P, P, P, P, P, I, I, I, I, I, I, P],
+    "hb_stream_add": [P, P, I, P, I, P, P, c_longlong, I, P],
+    "hb_rmsnorm_mean2": [P, P, I, P, P, I, F, P, I, I, I, P],
+    "hb_sigmoid_attention": [P, I, P, P, P, I, P, P, P, P, I, I, P, I, I, I, I, I, I, I, F, I, I, P, P],
+    "hb_gla_prep": [P, I, c_longlong, I, I, I, P, P, F, F, P, P, P, P, I, I, I, P],
     "hb_head_gate": [P, P, c_longlong, P, I, I, I, I, P],
     "hb_delta_prep": [P, I, c_longlong, I, I, P, P, c_longlong, c_longlong, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I,
-                      I, I, I, P],
+                      I, I, I, I, P],
     "hb_delta_conv_update": [P, I, c_longlong, I, P, c_longlong, c_longlong, P, P, I, I, I, P],
-    "hb_delta_recurrence": [P, P, P, P, P, P, c_longlong, P, P, P, I, I, I, I, I, I, I, P],
-    "hb_delta_out_norm": [P, P, I, P, F, P, I, c_longlong, I, P],
+    "hb_delta_recurrence": [P, P, P, P, P, P, c_longlong, P, P, P, I, I, I, I, I, I, I, I, P],
+    "hb_delta_out_norm": [P, P, I, P, F, P, I, c_longlong, I, I, c_longlong, I, P],
     "hb_mlstm_gates": [P, P, P, F, P, c_longlong, c_longlong, P, P, P, P, P, I, I, P],
     "hb_mlstm_recurrence": [P, I, c_longlong, I, I, I, F, P, P, P, c_longlong, P, P, P, P, I, I, I, I, I, P],
     "hb_mlstm_out_norm": [P, P, P, P, I, c_longlong, I, P, I, F, P, I, c_longlong, I, I, P],
@@ -155,8 +162,9 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional
                 out_dtype: torch.dtype, row_map: Optional[torch.Tensor] = None, also_f32: bool = False,
                 routed: Optional[torch.Tensor] = None, slot_of_entry: Optional[torch.Tensor] = None,
                 top_k: int = 0, routed_weight: Optional[torch.Tensor] = None, x_scale: float = 1.0,
-                post: bool = False):
-    """``x = x_scale * x + delta`` (float32, in place) then ``rmsnorm(x) * weight`` in ``out_dtype``.
+                post: bool = False, delta2: Optional[torch.Tensor] = None):
+    """``x = x_scale * x + delta (+ delta2)`` (float32, in place) then ``rmsnorm(x) * weight`` in ``out_dtype``.
+    ``delta2``: a second sub-layer result of the same shape (two sub-layers side by side on one input).
 
     ``post``: the norm comes after the sum in the block, so the stream itself takes the normalised rows
     (unrounded float32) instead of the sum; the returned ``y`` is the same rows in ``out_dtype``.
@@ -178,6 +186,10 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional
         _need(delta, "delta")
         if delta.shape != x.shape:
             raise KernelError(f"delta shape {tuple(delta.shape)} != residual shape {tuple(x.shape)}")
+    if delta2 is not None:
+        _need(delta2, "delta2")
+        if delta2.shape != x.shape:
+            raise KernelError(f"delta2 shape {tuple(delta2.shape)} != residual shape {tuple(x.shape)}")
     if weight is not None:
         _need(weight, "weight")
         if weight.numel() != hidden:
@@ -200,7 +212,8 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional
             _need(routed_weight, "routed_weight", torch.float32)
             if routed_weight.numel() != slot_of_entry.numel():
                 raise KernelError("routed_weight needs one factor per routing entry")
-    _check(lib().hb_add_rmsnorm(_ptr(x), _ptr(delta), _dt(delta) if delta is not None else 0, _ptr(routed),
+    _check(lib().hb_add_rmsnorm(_ptr(x), _ptr(delta), _dt(delta) if delta is not None else 0,
+                                _ptr(delta2), _dt(delta2) if delta2 is not None else 0, _ptr(routed),
                                 _ptr(slot_of_entry), _ptr(routed_weight) if routed is not None else None, int(top_k),
                                 _ptr(weight),
                                 _dt(weight) if weight is not None else 0, _ptr(y), _dt(y), _ptr(y32), _ptr(row_map),
@@ -329,20 +342,127 @@ def _row_strided(t: torch.Tensor, name: str) -> int:
 
 
 def latent_append(x: torch.Tensor, weight: torch.Tensor, eps: float, positions: torch.Tensor,
-                  seq_of_token: torch.Tensor, block_table: torch.Tensor, pages: torch.Tensor) -> None:
+                  seq_of_token: torch.Tensor, block_table: torch.Tensor, pages: torch.Tensor,
+                  inv_freq: Optional[torch.Tensor] = None, interleaved: bool = False) -> None:
     """pages[page of token, 0, place, :rank] = x / sqrt(mean(x^2) + eps) * weight for every token's row of
     ``x`` [N, rank] (rows may be a column slice of a wider matrix); ``pages`` [P, 1, page_size, row_len >= rank],
-    the rest of a row is zero-filled. Statistics in float32."""
+    the rest of a row is zero-filled. Statistics in float32.
+
+    With ``inv_freq`` (float32 [pairs]) ``x`` is [N, rank + 2 * pairs]: the columns behind the latent are a key
+    part that is not normed but rotated by the token's position (pairs (i, i + pairs), or (2i, 2i + 1) with
+    ``interleaved``) and written behind the latent in the page row."""
     stride = _row_strided(x, "x")
     _need(weight, "weight", x.dtype); _need(pages, "pages", x.dtype)
     for t, nm in ((positions, "positions"), (seq_of_token, "seq_of_token"), (block_table, "block_table")):
         _need(t, nm, torch.int32)
-    n, rank = x.shape
-    if pages.dim() != 4 or pages.shape[1] != 1 or pages.shape[3] < rank or weight.numel() != rank:
-        raise KernelError(f"pages {tuple(pages.shape)} / weight do not take latents of {rank}")
+    pairs = 0
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32)
+        pairs = inv_freq.numel()
+    n, rank = x.shape[0], x.shape[1] - 2 * pairs
+    if rank <= 0 or pages.dim() != 4 or pages.shape[1] != 1 or pages.shape[3] < x.shape[1] or weight.numel() != rank:
+        raise KernelError(f"pages {tuple(pages.shape)} / weight do not take latents of {rank} (+ {2 * pairs} rotated)")
     _check(lib().hb_latent_append(_ptr(x), _dt(x), stride, _ptr(weight), float(eps), _ptr(positions), _ptr(seq_of_token),
                                   _ptr(block_table), block_table.shape[1], _ptr(pages), pages.shape[2], rank,
-                                  pages.shape[3], n, _stream()), "latent_append")
+                                  pages.shape[3], n, _ptr(inv_freq), pairs, int(interleaved), _stream()), "latent_append")
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """x / sqrt(mean(x^2) + eps) * weight row by row (statistics in float32); ``x`` [N, W] may be a column slice
+    of a wider matrix. The result is contiguous, of x's dtype."""
+    stride = _row_strided(x, "x")
+    _need(weight, "weight", x.dtype)
+    n, width = x.shape
+    if weight.numel() != width:
+        raise KernelError(f"norm weight has {weight.numel()} elements for rows of {width}")
+    out = torch.empty((n, width), dtype=x.dtype, device=x.device)
+    _check(lib().hb_rmsnorm_rows(_ptr(x), _dt(x), stride, _ptr(weight), float(eps), _ptr(out), n, width, _stream()),
+           "rmsnorm_rows")
+    return out
+
+
+def rope_copy(src: torch.Tensor, dst: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+              interleaved: bool = False) -> None:
+    """dst[t, h, :2p] = src[t, h, :2p] rotated by positions[t] (p = len(inv_freq) pairs; (i, i + p), or
+    (2i, 2i + 1) with ``interleaved``). ``src`` and ``dst`` are [N, heads, >= 2p] views whose last axis is
+    contiguous (slices of wider tensors), of one dtype; they may be the same memory."""
+    _need(positions, "positions", torch.int32); _need(inv_freq, "inv_freq", torch.float32)
+    pairs = inv_freq.numel()
+    for t, nm in ((src, "src"), (dst, "dst")):
+        if not t.is_cuda or t.dim() != 3 or t.shape[2] < 2 * pairs or (t.shape[2] > 1 and t.stride(2) != 1):
+            raise KernelError(f"{nm} must be a CUDA view [N, heads, >= {2 * pairs}] with a contiguous last axis")
+    if src.dtype != dst.dtype or src.shape[:2] != dst.shape[:2] or positions.numel() != src.shape[0]:
+        raise KernelError("src and dst need one dtype and the same tokens and heads")
+    _check(lib().hb_rope_copy(_ptr(src), src.stride(0), src.stride(1), _ptr(dst), dst.stride(0), dst.stride(1), _dt(src),
+                              _ptr(positions), _ptr(inv_freq), src.shape[0], src.shape[1], pairs, int(interleaved),
+                              _stream()), "rope_copy")
+
+
+# --------------------------------------------------------------------------- convolved norm output, passes, two mixers
+def canon_conv(h: torch.Tensor, taps_a: torch.Tensor, taps_b: Optional[torch.Tensor], state: torch.Tensor,
+               cu_seqlens: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor, out_dtype: torch.dtype,
+               update_state: bool = True):
+    """y[t] = h[t] + sum_j taps[:, j] * h[t - (K-1) + j] over time within each request, for ``taps_a`` and (if
+    given) ``taps_b`` (float32 [W, K]); ``h`` float32 [N, W]. Rows before a portion's first token come from
+    ``state[slot]`` (float32 [K-1, W] flat: the last K-1 rows of h the request has seen; zeros at its start),
+    which then takes the portion's last rows. Returns (y_a, y_b | None) in ``out_dtype``."""
+    _need(h, "h", torch.float32); _need(taps_a, "taps_a", torch.float32); _need(state, "state", torch.float32)
+    for t, nm in ((cu_seqlens, "cu_seqlens"), (seq_of_token, "seq_of_token"), (slots, "slots")):
+        _need(t, nm, torch.int32)
+    n, width = h.shape
+    k = taps_a.shape[1]
+    if tuple(taps_a.shape) != (width, k) or (taps_b is not None and taps_b.shape != taps_a.shape):
+        raise KernelError("taps must be [width, K]")
+    if taps_b is not None:
+        _need(taps_b, "taps_b", torch.float32)
+    if state.dim() != 2 or state.shape[1] < (k - 1) * width:
+        raise KernelError("the state does not hold K-1 rows of the width")
+    out_a = torch.empty((n, width), dtype=out_dtype, device=h.device)
+    out_b = torch.empty_like(out_a) if taps_b is not None else None
+    _check(lib().hb_canon_conv(_ptr(h), _ptr(taps_a), _ptr(taps_b), _ptr(state), state.shape[1], _ptr(cu_seqlens),
+                               _ptr(seq_of_token), _ptr(slots), _ptr(out_a), _ptr(out_b), _dt(out_a), n, slots.numel(),
+                               width, k, int(update_state), _stream()), "canon_conv")
+    if update_state and k > 1:
+        LAUNCHES[0] += 1
+    return out_a, out_b
+
+
+def stream_add(x: torch.Tensor, d1: Optional[torch.Tensor] = None, d2: Optional[torch.Tensor] = None,
+               rows_f32: Optional[torch.Tensor] = None, vector: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x += d1 + d2 + rows_f32 + vector (broadcast over rows), in place on the float32 stream [N, W]; any term
+    may be absent. ``d1``/``d2`` [N, W] float32 or bfloat16, ``rows_f32`` float32 [N, W], ``vector`` float32 [W]."""
+    _need(x, "x", torch.float32)
+    n, width = x.shape
+    for t, nm in ((d1, "d1"), (d2, "d2")):
+        if t is not None:
+            _need(t, nm)
+            if t.shape != x.shape:
+                raise KernelError(f"{nm} does not match the stream")
+    if rows_f32 is not None:
+        _need(rows_f32, "rows_f32", torch.float32)
+        if rows_f32.shape != x.shape:
+            raise KernelError("rows_f32 does not match the stream")
+    if vector is not None:
+        _need(vector, "vector", torch.float32)
+        if vector.numel() != width:
+            raise KernelError("vector needs one entry per column")
+    _check(lib().hb_stream_add(_ptr(x), _ptr(d1), _dt(d1) if d1 is not None else 0, _ptr(d2),
+                               _dt(d2) if d2 is not None else 0, _ptr(rows_f32), _ptr(vector), n, width, _stream()),
+           "stream_add")
+    return x
+
+
+def rmsnorm_mean2(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float,
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """(a / rms(a) * wa + b / rms(b) * wb) / 2 row by row, statistics in float32; a, b [N, W] of one dtype."""
+    _need(a, "a"); _need(b, "b", a.dtype); _need(wa, "wa"); _need(wb, "wb", wa.dtype)
+    n, width = a.shape
+    if b.shape != a.shape or wa.numel() != width or wb.numel() != width:
+        raise KernelError("the two inputs and their weights must match")
+    out = torch.empty((n, width), dtype=out_dtype, device=a.device)
+    _check(lib().hb_rmsnorm_mean2(_ptr(a), _ptr(b), _dt(a), _ptr(wa), _ptr(wb), _dt(wa), float(eps), _ptr(out), _dt(out),
+                                  n, width, _stream()), "rmsnorm_mean2")
+    return out
 
 
 def head_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
@@ -361,12 +481,14 @@ def head_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
 def delta_prep(proj: torch.Tensor, chan_off: int, beta_off: int, taps: torch.Tensor, state: torch.Tensor,
                conv_off: int, a_pre: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
                cu_seqlens: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor, heads: int, kvh: int,
-               dim: int, vdim: int):
+               dim: int, vdim: int, head_decay: bool = False):
     """Per token: causal convolution over time (``taps`` float32 [C, K], last column = the token itself) and
     silu of the C = 2*kvh*dim + heads*vdim channels q | k | v that start at column ``chan_off`` of ``proj``
     [N, ld]; rows before a portion's first token come from ``state[slot, conv_off:]`` ([K-1, C] float32);
     q and k to unit length per head (q also * dim^-1/2); beta = sigmoid(proj[:, beta_off + h]);
-    decay = exp(-exp(a_log[h]) * softplus(a_pre + dt_bias)). Returns float32 (q, k, v, beta, decay)."""
+    decay = exp(-exp(a_log[h]) * softplus(a_pre + dt_bias)). Returns float32 (q, k, v, beta, decay).
+    ``head_decay``: one decay per head (``a_pre`` [N, heads], ``dt_bias`` [heads]), written out for every key
+    channel of the head, so ``decay`` is [N, heads * dim] either way."""
     _need(proj, "proj"); _need(taps, "taps", torch.float32); _need(state, "state", torch.float32)
     _need(a_pre, "a_pre"); _need(dt_bias, "dt_bias", torch.float32); _need(a_log, "a_log", torch.float32)
     for t, nm in ((cu_seqlens, "cu_seqlens"), (seq_of_token, "seq_of_token"), (slots, "slots")):
@@ -376,8 +498,9 @@ def delta_prep(proj: torch.Tensor, chan_off: int, beta_off: int, taps: torch.Ten
     k_taps = taps.shape[1]
     if tuple(taps.shape) != (c, k_taps) or chan_off + c > ld or beta_off + heads > ld:
         raise KernelError("taps / column offsets do not fit the projection")
-    if tuple(a_pre.shape) != (n, heads * dim) or dt_bias.numel() != heads * dim or a_log.numel() != heads:
-        raise KernelError("decay inputs do not match heads x dim")
+    per = heads if head_decay else heads * dim
+    if tuple(a_pre.shape) != (n, per) or dt_bias.numel() != per or a_log.numel() != heads:
+        raise KernelError("decay inputs do not match heads (x dim)")
     if state.dim() != 2 or conv_off + (k_taps - 1) * c > state.shape[1]:
         raise KernelError("the state does not hold the convolution's inputs")
     dev, f32 = proj.device, torch.float32
@@ -389,7 +512,7 @@ def delta_prep(proj: torch.Tensor, chan_off: int, beta_off: int, taps: torch.Ten
     _check(lib().hb_delta_prep(_ptr(proj), _dt(proj), ld, int(chan_off), int(beta_off), _ptr(taps), _ptr(state),
                                state.shape[1], int(conv_off), _ptr(a_pre), _dt(a_pre), _ptr(dt_bias), _ptr(a_log),
                                _ptr(cu_seqlens), _ptr(seq_of_token), _ptr(slots), _ptr(q), _ptr(k), _ptr(v), _ptr(beta),
-                               _ptr(decay), n, heads, kvh, dim, vdim, k_taps, _stream()), "delta_prep")
+                               _ptr(decay), n, heads, kvh, dim, vdim, k_taps, int(head_decay), _stream()), "delta_prep")
     return q, k, v, beta, decay
 
 
@@ -405,41 +528,69 @@ def delta_conv_update(proj: torch.Tensor, chan_off: int, channels: int, taps_n: 
                                       _stream()), "delta_conv_update")
 
 
-def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor,
-                     state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, heads: int, kvh: int,
-                     dim: int, vdim: int, general: bool = False, rows: int = 0, single_tokens: bool = False) -> torch.Tensor:
+def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: Optional[torch.Tensor],
+                     decay: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, heads: int,
+                     kvh: int, dim: int, vdim: int, general: bool = False, rows: int = 0, single_tokens: bool = False,
+                     plain: bool = False) -> torch.Tensor:
     """Token after token per request and head, on ``state[slot, :heads*dim*vdim]`` ([heads, dim, vdim] float32):
     S <- decay * S (per row); u = beta (v - S^T k); S <- S + k u^T; o = S^T q. Returns o float32 [N, heads*vdim].
     ``general`` forces the kernel that keeps S in shared memory (any dim) instead of registers (dim <= 256);
     ``rows`` (16, 32) forces how many rows of a column a lane holds, else ``single_tokens`` (every request
-    brings one token) decides: the order of the sums differs between the forms, by rounding only."""
-    for t, nm in ((q, "q"), (k, "k"), (v, "v"), (beta, "beta"), (decay, "decay"), (state, "state")):
+    brings one token) decides: the order of the sums differs between the forms, by rounding only.
+    ``plain``: the rule without the correction, S <- decay * S + k v^T; o = S^T q (``beta`` is not read)."""
+    for t, nm in ((q, "q"), (k, "k"), (v, "v"), (decay, "decay"), (state, "state")) + (() if plain else ((beta, "beta"),)):
         _need(t, nm, torch.float32)
     _need(cu_seqlens, "cu_seqlens", torch.int32); _need(slots, "slots", torch.int32)
     n = q.shape[0]
     if tuple(q.shape) != (n, kvh * dim) or tuple(k.shape) != (n, kvh * dim) or tuple(v.shape) != (n, heads * vdim) or \
-            tuple(beta.shape) != (n, heads) or tuple(decay.shape) != (n, heads * dim):
+            (not plain and tuple(beta.shape) != (n, heads)) or tuple(decay.shape) != (n, heads * dim):
         raise KernelError("q / k / v / beta / decay do not match the head sizes")
     if state.dim() != 2 or state.shape[1] < heads * dim * vdim or cu_seqlens.numel() != slots.numel() + 1:
         raise KernelError("the state or the request tables do not fit")
     out = torch.empty((n, heads * vdim), dtype=torch.float32, device=q.device)
-    _check(lib().hb_delta_recurrence(_ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(state), state.shape[1],
-                                     _ptr(cu_seqlens), _ptr(slots), _ptr(out), slots.numel(), heads, kvh, dim, vdim,
-                                     1 if general else int(rows), int(single_tokens), _stream()), "delta_recurrence")
+    _check(lib().hb_delta_recurrence(_ptr(q), _ptr(k), _ptr(v), None if plain else _ptr(beta), _ptr(decay), _ptr(state),
+                                     state.shape[1], _ptr(cu_seqlens), _ptr(slots), _ptr(out), slots.numel(), heads, kvh,
+                                     dim, vdim, 1 if general else int(rows), int(single_tokens), int(plain), _stream()),
+           "delta_recurrence")
     return out
 
 
 def delta_out_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, vdim: int,
-                   out_dtype: torch.dtype) -> torch.Tensor:
+                   out_dtype: torch.dtype, gate_silu: bool = False) -> torch.Tensor:
     """o [N, heads*vdim] float32 -> o / sqrt(mean over each head's vdim (o^2) + eps) * weight[vdim] *
-    sigmoid(gate), in ``out_dtype``."""
-    _need(o, "o", torch.float32); _need(gate, "gate"); _need(weight, "weight", out_dtype)
+    sigmoid(gate) (``gate_silu``: * gate sigmoid(gate)), in ``out_dtype``. ``gate`` may be a column slice."""
+    _need(o, "o", torch.float32); _need(weight, "weight", out_dtype)
+    gate_stride = _row_strided(gate, "gate")
     if o.shape != gate.shape or o.shape[1] % vdim or weight.numel() != vdim:
         raise KernelError("gate / weight do not match the heads' value size")
     out = torch.empty(o.shape, dtype=out_dtype, device=o.device)
     _check(lib().hb_delta_out_norm(_ptr(o), _ptr(gate), _dt(gate), _ptr(weight), float(eps), _ptr(out), _dt(out),
-                                   o.numel() // vdim, vdim, _stream()), "delta_out_norm")
+                                   o.numel() // vdim, vdim, int(gate_silu), gate_stride, o.shape[1] // vdim, _stream()),
+           "delta_out_norm")
     return out
+
+
+def gla_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, z: torch.Tensor, bias: Optional[torch.Tensor],
+             tau: float, q_scale: float, qk_cols: int, v_cols: int):
+    """Inputs of the recurrence without correction from a projection's columns: q * q_scale, k [N, qk_cols] and
+    v [N, v_cols] as float32, and decay = sigmoid(z + bias)^(1 / tau) [N, qk_cols] (``z`` float32)."""
+    _need(proj, "proj"); _need(z, "z", torch.float32)
+    n, ld = proj.shape
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != qk_cols:
+            raise KernelError("one bias per key channel")
+    if tuple(z.shape) != (n, qk_cols) or max(q_off, k_off) + qk_cols > ld or v_off + v_cols > ld:
+        raise KernelError("columns do not fit the projection")
+    dev, f32 = proj.device, torch.float32
+    q = torch.empty((n, qk_cols), dtype=f32, device=dev)
+    k = torch.empty((n, qk_cols), dtype=f32, device=dev)
+    v = torch.empty((n, v_cols), dtype=f32, device=dev)
+    decay = torch.empty((n, qk_cols), dtype=f32, device=dev)
+    _check(lib().hb_gla_prep(_ptr(proj), _dt(proj), ld, int(q_off), int(k_off), int(v_off), _ptr(z), _ptr(bias),
+                             float(tau), float(q_scale), _ptr(q), _ptr(k), _ptr(v), _ptr(decay), n, qk_cols, v_cols,
+                             _stream()), "gla_prep")
+    return q, k, v, decay
 
 
 # --------------------------------------------------------------------------- mLSTM matrix memory
@@ -547,13 +698,16 @@ def qkv_post(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positions: torch.Ten
              block_table: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
              v_pages: Optional[torch.Tensor], page_size: int, write_kv: bool,
              q_norm_weight: Optional[torch.Tensor] = None, k_norm_weight: Optional[torch.Tensor] = None,
-             norm_first: bool = False, norm_dim: int = 0, rot_mul: float = 1.0) -> torch.Tensor:
+             norm_first: bool = False, norm_dim: int = 0, rot_mul: float = 1.0,
+             v_inv_freq: Optional[torch.Tensor] = None, v_interleaved: bool = False) -> torch.Tensor:
     """Rotary or temperature, optional L2 norm, and the cache append; returns q [N, nh, hd].
 
     By default the norm of q and k is weightless and comes after the rotation. ``norm_first``: it comes
     before, over the first ``norm_dim`` dims of a head (0: all; dims past them are padding), times
     ``q_norm_weight`` / ``k_norm_weight`` (float32 [hd], shared by the heads). ``rot_mul`` multiplies
     cos and sin. Any even number of rotating dims is taken then (a general kernel runs these forms).
+    ``v_inv_freq`` (float32 [pairs]): the values are cached rotated by their own position, pair m of their first
+    2 * pairs dims by position * v_inv_freq[m] (pairs (m, m + pairs), or (2m, 2m + 1) with ``v_interleaved``).
 
     ``qkv`` is [N, (nh + 2*nkv) * hd]; ``k_pages``/``v_pages`` are [pages, nkv, page_size, hd];
     ``block_table`` [S, width] int32 maps (sequence row, position // page_size) to a page.
@@ -562,10 +716,16 @@ def qkv_post(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positions: torch.Ten
     n = qkv.shape[0]
     if qkv.shape[1] != (nh + 2 * nkv) * hd:
         raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {(nh + 2 * nkv) * hd}")
-    general = norm_first or q_norm_weight is not None or k_norm_weight is not None or rot_mul != 1.0 or \
+    general = v_inv_freq is not None or norm_first or q_norm_weight is not None or k_norm_weight is not None or rot_mul != 1.0 or \
         (norm_dim not in (0, hd)) or (inv_freq is not None and inv_freq.numel() % 8 != 0)
     if hd % 8 != 0 or hd > 512 or (not general and (hd % 16 != 0 or hd > 256)):
         raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 256; the general form: of 8 up to 512)")
+    v_pairs = 0
+    if v_inv_freq is not None:
+        _need(v_inv_freq, "v_inv_freq", torch.float32)
+        v_pairs = v_inv_freq.numel()
+        if 2 * v_pairs > hd:
+            raise KernelError("more rotating value dims than a head has")
     if general:
         rot_pairs = 0 if inv_freq is None else inv_freq.numel()
         if inv_freq is not None:
@@ -589,7 +749,8 @@ def qkv_post(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positions: torch.Ten
     fs, asc = temperature if temperature is not None else (1.0, 0.0)
     _check(lib().hb_qkv_post(_ptr(qkv), _dt(qkv), _ptr(inv_freq), rot_pairs, int(interleaved), int(qk_norm),
                              float(qk_eps), int(temperature is not None), float(fs), float(asc), _ptr(q_norm_weight),
-                             _ptr(k_norm_weight), int(norm_first), int(norm_dim), float(rot_mul), _ptr(positions),
+                             _ptr(k_norm_weight), int(norm_first), int(norm_dim), float(rot_mul), _ptr(v_inv_freq),
+                             v_pairs, int(v_interleaved), _ptr(positions),
                              _ptr(seq_of_token), _ptr(block_table), stride, _ptr(q), _ptr(k_pages), _ptr(v_pages),
                              page_size, int(write_kv), n, nh, nkv, hd, _stream()), "qkv_post")
     return q
@@ -647,6 +808,47 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                                     hd, page_size, int(chunk), int(window), float(scale), int(sink), ATTENTION_SPLIT,
                                     splits, _ptr(part_acc), _ptr(part_ml), _stream()),
            "paged_attention")
+    return out
+
+
+def sigmoid_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                      seq_of_token: torch.Tensor, positions: torch.Tensor, chunk: int, window: int, scale: float,
+                      head_bias: Optional[torch.Tensor], max_context: int = 0,
+                      v_inv_freq: Optional[torch.Tensor] = None, v_interleaved: bool = False) -> torch.Tensor:
+    """sum_j sigmoid(q . k_j * scale + head_bias[h]) v_j over the keys each token may read (no normalisation);
+    q [N, nh, hd] -> [N, nh, hd]. With ``v_inv_freq`` the cached values are taken as rotated by their positions
+    and every head's sum is turned back by the query's position (see :func:`qkv_post`). Long ranges are cut into
+    splits of ``ATTENTION_SPLIT`` keys as in :func:`paged_attention`; the splits add."""
+    _need(q, "q"); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
+    for t, nm in ((block_table, "block_table"), (seq_of_token, "seq_of_token"), (positions, "positions")):
+        _need(t, nm, torch.int32)
+    n, nh, hd = q.shape
+    _, nkv, page_size, hd2 = k_pages.shape
+    if hd2 != hd or k_pages.shape != v_pages.shape or nh % nkv:
+        raise KernelError("cache pages do not match the query's heads")
+    if hd % 8 != 0 or hd > 512:
+        raise KernelError(f"head_dim {hd} is not supported (multiples of 8 up to 512)")
+    if head_bias is not None:
+        _need(head_bias, "head_bias", torch.float32)
+        if head_bias.numel() != nh:
+            raise KernelError("one bias per query head")
+    v_pairs = 0
+    if v_inv_freq is not None:
+        _need(v_inv_freq, "v_inv_freq", torch.float32)
+        v_pairs = v_inv_freq.numel()
+    out = torch.empty_like(q)
+    longest = max_context
+    if chunk > 0:
+        longest = min(longest, chunk)
+    if window > 0:
+        longest = min(longest, window)
+    splits = max(1, -(-longest // ATTENTION_SPLIT))
+    part_acc = torch.empty((n, nh, splits, hd), dtype=torch.float32, device=q.device) if splits > 1 else None
+    _check(lib().hb_sigmoid_attention(_ptr(q), _dt(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                                      block_table.shape[1], _ptr(seq_of_token), _ptr(positions), _ptr(head_bias),
+                                      _ptr(v_inv_freq), v_pairs, int(v_interleaved), _ptr(out), n, nh, nkv, hd,
+                                      page_size, int(chunk), int(window), float(scale), ATTENTION_SPLIT, splits,
+                                      _ptr(part_acc), _stream()), "sigmoid_attention")
     return out
 
 

@@ -3,6 +3,7 @@ from __future__ import annotations
 
 from typing import Optional
 
+import numpy as np
 import torch
 
 from ..kernels import ops
@@ -103,6 +104,11 @@ class AttentionMixer(Part):
       ``sink``         the softmax's denominator has one more term of score 0: exp(s_j) / (1 + sum exp(s_j))
       ``names``        "proj" (default): ``<prefix>.{q,k,v,o}_proj.weight`` / ``.bias``;
                        "short": ``<prefix>.{q,k,v,o}`` and ``<prefix>.{q,k,v,o}.b``
+      ``weights``      "softmax" (default) | "sigmoid": the weight of a visible key is sigmoid(score + pb[head]),
+                       ``<prefix>.pb`` [heads], and the weights are not normalised over the keys
+      ``value_rotation``  None | {"base": b, "interleaved": bool}: the value of position j is cached rotated by j
+                       over all its dims (pair m by j * b^(-2m / value_dim)) and each head's sum at position i is
+                       turned back by i, so a value's weight in the output also depends on i - j
     tensors: the four projections, and each projection's bias where the checkpoint has one (a bias is
     used iff its tensor exists: crates/hi-mlx/src/models.rs:1808, 1843-1845).
     """
@@ -120,6 +126,13 @@ class AttentionMixer(Part):
         self.dim, self.vdim = self.hd, int(p.get("value_dim") or self.hd)      # sizes as the checkpoint has them
         self.norm_weighted = bool(p.get("qk_norm_weighted", False))
         self.sink = bool(p.get("sink", False))
+        self.sigmoid = p.get("weights", "softmax") == "sigmoid"
+        if p.get("weights", "softmax") not in ("softmax", "sigmoid") or (self.sigmoid and self.sink):
+            raise ValueError(f"{prefix}: weights are 'softmax' or 'sigmoid' (which has no sink)")
+        self.value_rotation = dict(p["value_rotation"]) if p.get("value_rotation") else None
+        if self.value_rotation and not self.sigmoid:
+            raise ValueError(f"{prefix}: rotated values are built for sigmoid weights only")
+        self.head_bias = self._v_table = None
         self.short_names = p.get("names", "proj") == "short"
         if self.dim != self.vdim or self.dim % 16:
             self.hd = -(-max(self.dim, self.vdim) // 16) * 16                  # rows of the cache and of q
@@ -156,6 +169,8 @@ class AttentionMixer(Part):
                   for n in "qkvo"]
         if self.norm_weighted:
             specs += [TensorSpec(f"{self.prefix}.{n}.norm", (self.dim,), init="ones") for n in "qk"]
+        if self.sigmoid:
+            specs.append(TensorSpec(f"{self.prefix}.pb", (self.nh,)))
         return specs
 
     def _pad_heads(self, t, heads: int, size: int):
@@ -190,6 +205,14 @@ class AttentionMixer(Part):
                 w[: self.dim] = fetch(f"{self.prefix}.{n}.norm").to(torch.float32)
                 return w
             self.w_qnorm, self.w_knorm = weight("q"), weight("k")
+        if self.sigmoid:
+            self.head_bias = fetch(f"{self.prefix}.pb").to(torch.float32).contiguous()
+        if self.value_rotation:
+            if self.vdim % 2:
+                raise ValueError(f"{self.prefix}: rotated values need an even value size")
+            base = float(self.value_rotation["base"])
+            table = np.array([base ** (-2.0 * m / self.vdim) for m in range(self.vdim // 2)], dtype=np.float64)
+            self._v_table = torch.from_numpy(table.astype(np.float32)).to(self.w_qkv.device)
 
     def forward(self, normed, ctx, cache):
         qkv = linear(normed, self.w_qkv, bias=self.b_qkv)
@@ -207,6 +230,18 @@ class AttentionMixer(Part):
         sliding = self.window[1] if self.window and self.window[0] == "sliding" else 0
         rot_mul = float(getattr(self.position, "magnitude", 1.0))
         plain = not (self.norm_weighted or self.sink or self.hd != self.dim or rot_mul != 1.0)
+        if self.sigmoid:
+            v_inter = bool(self.value_rotation and self.value_rotation.get("interleaved", False))
+            q = ops.qkv_post(qkv, self.nh, self.nkv, self.hd, positions, inv_freq, interleaved, self.qk_norm,
+                             self.qk_norm_eps, self.temperature, ctx.seq_of_token, block_table, cache.k_pages,
+                             cache.v_pages, ctx.page_size, cache.writes, q_norm_weight=self.w_qnorm,
+                             k_norm_weight=self.w_knorm, norm_first=self.norm_weighted,
+                             norm_dim=0 if plain else self.dim, rot_mul=rot_mul, v_inv_freq=self._v_table,
+                             v_interleaved=v_inter)
+            o = ops.sigmoid_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions, chunk,
+                                      sliding, self.scale, self.head_bias, ctx.max_context, v_inv_freq=self._v_table,
+                                      v_interleaved=v_inter)
+            return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o, bias=self.b_o)
         if self.hd == self.dim and ctx.max_new == 1 and cache.writes and self.FUSED_DECODE and qkv.dtype == torch.bfloat16:
             # a step of single decoded tokens: encoding, cache append, attention and the merge of its
             # splits in one launch, where the kernel takes the shapes

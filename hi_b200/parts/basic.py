@@ -35,6 +35,10 @@ class Part:
     def cache_spec(self):
         return None
 
+    def state_size(self) -> int:
+        """Block arrangements: float32 numbers the block keeps per request and cache slot (0: none)."""
+        return 0
+
 
 # --------------------------------------------------------------------------- norms
 @register("norm", "rmsnorm")
@@ -58,15 +62,19 @@ class RMSNorm(Part):
     def load(self, fetch):
         self.weight = fetch(self.tensor_name).contiguous()
 
-    def forward(self, residual: torch.Tensor, delta, row_map: Optional[torch.Tensor] = None, also_f32: bool = False):
-        """``delta``: None, a tensor, or a :class:`~hi_b200.parts.context.Pending`."""
+    def forward(self, residual: torch.Tensor, delta, row_map: Optional[torch.Tensor] = None, also_f32: bool = False,
+                out_dtype: Optional[torch.dtype] = None):
+        """``delta``: None, a tensor, or a :class:`~hi_b200.parts.context.Pending`. ``out_dtype``: the engine's
+        dtype, or float32 for a consumer that goes on in 32-bit."""
+        out_dtype = out_dtype or self.env.dtype
         if isinstance(delta, Pending):
             if delta.top_k > 8:
                 delta = delta.materialize(residual.shape[0])
             else:
-                return ops.add_rmsnorm(residual, delta.dense, self.weight, self.eps, self.env.dtype, row_map, also_f32,
-                                       delta.routed, delta.slot_of_entry, delta.top_k, delta.entry_weights)
-        return ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.env.dtype, row_map, also_f32)
+                return ops.add_rmsnorm(residual, delta.dense, self.weight, self.eps, out_dtype, row_map, also_f32,
+                                       delta.routed, delta.slot_of_entry, delta.top_k, delta.entry_weights,
+                                       delta2=delta.dense2)
+        return ops.add_rmsnorm(residual, delta, self.weight, self.eps, out_dtype, row_map, also_f32)
 
 
 @register("norm", "dynamic_tanh")
@@ -159,13 +167,33 @@ def llama3_inverse_frequencies(head_dim: int, theta: float, scaling: Optional[di
     return out
 
 
+def exact_inverse_frequencies(dims: int, theta: float, scaling: Optional[dict]) -> np.ndarray:
+    """The table of :func:`llama3_inverse_frequencies` (same keys of ``scaling``) worked out in float64 and
+    rounded to float32 once."""
+    out = np.empty(dims // 2, dtype=np.float64)
+    for j in range(dims // 2):
+        inv = float(theta) ** (-2.0 * j / dims)
+        if scaling:
+            factor, low = float(scaling["factor"]), float(scaling["low_freq_factor"])
+            high, orig = float(scaling["high_freq_factor"]), float(scaling["original_max_position_embeddings"])
+            wavelen = 2.0 * math.pi / inv
+            if wavelen > orig / low:
+                inv = inv / factor
+            elif wavelen >= orig / high:
+                smooth = 0.0 if high == low else (orig / wavelen - low) / (high - low)
+                inv = (1.0 - smooth) * inv / factor + smooth * inv
+        out[j] = inv
+    return out.astype(np.float32)
+
+
 @register("position", "rope")
 class RotaryPosition(Part):
     """Rotary encoding of q and k: all head_dim dims, or with ``rot_dim`` the first rot_dim of them
-    (a multiple of 16; the rest pass through).
+    (an even number; the rest pass through; whole lanes of 16 dims take the faster encoding kernel).
     params: ``head_dim``, ``theta``, ``scaling`` (dict or None), ``interleaved`` (pairs (2j, 2j+1)
     instead of (j, j + rot_dim/2)), ``rot_dim`` (default head_dim; the frequencies are
-    theta^(-2j/rot_dim))."""
+    theta^(-2j/rot_dim)), ``exact`` (the table is worked out in float64 and rounded once, instead of in
+    float32 step by step as the reference does)."""
 
     graph_safe = True
 
@@ -173,9 +201,12 @@ class RotaryPosition(Part):
         super().__init__(params, prefix, env)
         self.interleaved = bool(params.get("interleaved", False))
         self.rot_dim = int(params.get("rot_dim") or params["head_dim"])
-        if self.rot_dim % 16 or not 0 < self.rot_dim <= int(params["head_dim"]):
-            raise ValueError(f"{prefix}: rot_dim {self.rot_dim} must be a multiple of 16, at most head_dim")
-        self._table_host = llama3_inverse_frequencies(self.rot_dim, float(params["theta"]), params.get("scaling"))
+        if self.rot_dim % 2 or not 0 < self.rot_dim <= int(params["head_dim"]):
+            raise ValueError(f"{prefix}: rot_dim {self.rot_dim} must be even, at most head_dim")
+        if params.get("exact"):
+            self._table_host = exact_inverse_frequencies(self.rot_dim, float(params["theta"]), params.get("scaling"))
+        else:
+            self._table_host = llama3_inverse_frequencies(self.rot_dim, float(params["theta"]), params.get("scaling"))
         self._table: Optional[torch.Tensor] = None
 
     def rotary_table(self):
@@ -490,3 +521,101 @@ class ParallelGatedBlock(Part):
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         return x, GatedPending(terms=terms, history=history, filled=self.results_before, mix=self.mix)
+
+
+@register("arrangement", "parallel_conv")
+class ParallelConvBlock(Part):
+    """One norm; the mixer and the feed-forward both read its output, each through its own short causal
+    convolution over time, and their sum joins the stream:
+
+        h = norm1(x)
+        h_a = h + conv_a(h),  h_b = h + conv_b(h)      conv(h)[t] = sum_j taps[:, j] * h[t - (K-1) + j]
+        x <- x + mixer(h_a) + ff(h_b)
+
+    h stays float32 between the norm and the convolutions (one kernel for both, ``ops.canon_conv``); the two
+    results are carried as a ``Pending`` with two dense parts and summed into the stream by the next norm.
+    Per request and cache slot the block keeps the last K-1 rows of h (float32), zero at a sequence's start:
+    ``state_size``. A layer without feed-forward has the first branch only.
+
+    params: ``hidden_size``, ``taps`` (K >= 1), ``feed_forward`` (default True).
+    tensors: ``<prefix>.canon1`` [W, K] (mixer), ``<prefix>.canon2`` [W, K] (feed-forward). The norm must be ``rmsnorm``."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        self.width, self.taps = int(params["hidden_size"]), int(params["taps"])
+        if not 1 <= self.taps <= 8:
+            raise ValueError(f"{prefix}: {self.taps} taps are not supported (1 to 8)")
+        self.has_ff = bool(params.get("feed_forward", True))
+        self.taps_a = self.taps_b = self._no_state = None
+
+    def state_size(self) -> int:
+        return (self.taps - 1) * self.width
+
+    def tensor_specs(self):
+        names = ("canon1", "canon2") if self.has_ff else ("canon1",)
+        return [TensorSpec(f"{self.prefix}.{n}", (self.width, self.taps)) for n in names]
+
+    def load(self, fetch):
+        self.taps_a = fetch(f"{self.prefix}.canon1").to(torch.float32).contiguous()
+        if self.has_ff:
+            self.taps_b = fetch(f"{self.prefix}.canon2").to(torch.float32).contiguous()
+        self._no_state = torch.zeros((1, 1), dtype=torch.float32, device=self.taps_a.device)
+
+    def forward(self, layer, residual, pending, ctx, cache_view):
+        norm = layer.norm_mixer
+        if not isinstance(norm, RMSNorm):
+            raise TypeError(f"{self.prefix}: the block works with an rmsnorm norm")
+        h = norm.forward(residual, pending, out_dtype=torch.float32)
+        if ctx.tap is not None:
+            ctx.tap(f"{self.prefix}.stream_in", residual)        # debug: the stream as this layer reads it
+        state = cache_view.block_state if self.taps > 1 else self._no_state
+        if state is None:
+            raise RuntimeError(f"{self.prefix}: the block has no state rows for its convolutions")
+        h_a, h_b = ops.canon_conv(h, self.taps_a, self.taps_b, state, ctx.cu_seqlens, ctx.seq_of_token, ctx.slots,
+                                  self.env.dtype)
+        delta = layer.mixer.forward(h_a, ctx, cache_view)
+        if not self.has_ff:
+            return residual, Pending(dense=delta)
+        second = layer.feed_forward.forward(h_b, ctx)
+        if isinstance(second, Pending):
+            second = second.materialize(h_b.shape[0])
+        return residual, Pending(dense=delta, dense2=second)
+
+
+# --------------------------------------------------------------------------- between passes
+@register("interlude", "pass_offset")
+class PassOffset(Part):
+    """What a model adds to the stream right before a pass over a range of its layers that runs several times:
+    a learned vector per pass, and (``add_embedding``) before every pass but the first the embedding output
+    again. Whatever the layer before left open is summed into the stream by the same kernel.
+
+    params: ``hidden_size``, ``times``, ``add_embedding`` (default True); tensor ``<prefix>`` [times, W]."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        self.width, self.times = int(params["hidden_size"]), int(params["times"])
+        self.needs_embedding_output = bool(params.get("add_embedding", True)) and self.times > 1
+        self.table: Optional[torch.Tensor] = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.prefix, (self.times, self.width))]
+
+    def load(self, fetch):
+        self.table = fetch(self.prefix).to(torch.float32).contiguous()
+
+    def forward(self, residual, pending, ctx, arg: int):
+        d1 = d2 = None
+        if isinstance(pending, Pending):
+            if pending.routed is not None:
+                d1 = pending.materialize(residual.shape[0])
+            else:
+                d1, d2 = pending.dense, pending.dense2
+        elif pending is not None:
+            d1 = pending
+        again = ctx.scratch["embedding_output"] if self.needs_embedding_output and arg > 0 else None
+        ops.stream_add(residual, d1, d2, again, self.table[arg])
+        return residual, None

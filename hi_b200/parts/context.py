@@ -56,6 +56,7 @@ class CacheView:
     state: Optional[torch.Tensor] = None         # [max_slots, *state_shape]
     writes: bool = True                          # False: read another entry's cache, do not append
     slot: Optional[int] = None                   # the cache slot's number (a key for per-pass scratch)
+    block_state: Optional[torch.Tensor] = None   # [max_slots, n] float32: fixed-size state of the block arrangement
 
 
 @dataclass
@@ -66,6 +67,7 @@ class Pending:
     it in one pass."""
 
     dense: Optional[torch.Tensor] = None
+    dense2: Optional[torch.Tensor] = None            # a second dense part (two sub-layers side by side)
     routed: Optional[torch.Tensor] = None
     slot_of_entry: Optional[torch.Tensor] = None
     top_k: int = 0
@@ -75,6 +77,12 @@ class Pending:
         """The sum as one float32 tensor, for a consumer that is not a norm."""
         from ..kernels import ops
 
+        if self.dense2 is not None:
+            total = torch.zeros((n_tokens, self.dense.shape[1]), dtype=torch.float32, device=self.dense.device)
+            ops.stream_add(total, self.dense, self.dense2)
+            if self.routed is None:
+                return total
+            return ops.moe_combine(self.routed, self.slot_of_entry, total, n_tokens, self.top_k, self.entry_weights)
         if self.routed is None:
             return self.dense
         return ops.moe_combine(self.routed, self.slot_of_entry, self.dense, n_tokens, self.top_k, self.entry_weights)

@@ -11,6 +11,7 @@ from .registry import register
 from .spec import CacheSpec, TensorSpec
 
 
+@register("mixer", "gated_delta")
 @register("mixer", "channel_delta")
 class ChannelDeltaMixer(Part):
     """Per head a matrix S [dim, vdim] that every token decays row by row, corrects towards its value
@@ -29,7 +30,11 @@ class ChannelDeltaMixer(Part):
     float32 (``ops.delta_prep``, ``ops.delta_recurrence``, ``ops.delta_out_norm``).
 
     params: ``hidden_size``, ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``conv`` (taps), ``decay_rank`` and
-    ``gate_rank`` (inner sizes of the two low-rank maps), ``eps`` (of the output norm).
+    ``gate_rank`` (inner sizes of the two low-rank maps), ``eps`` (of the output norm);
+    ``decay_per`` "channel" (default, as above) | "head": one decay per head,
+    g = exp(-exp(A_log) * softplus(W_a h + dt_bias)) with ``<prefix>.a`` [heads, H] and ``dt_bias`` [heads] (no a1 / a2);
+    ``gate`` "low_rank_sigmoid" (default, as above) | "silu": the output is multiplied by silu(W_g h) with
+    ``<prefix>.g`` [heads*vdim, H] (no g1 / g2).
     tensors: ``<prefix>.{q,k,v}`` and ``<prefix>.{q,k,v}.conv`` [channels, taps], ``<prefix>.b`` [heads, H],
     ``<prefix>.A_log`` [heads], ``<prefix>.a1`` [r, H], ``<prefix>.a2`` [heads*dim, r], ``<prefix>.dt_bias``
     [heads*dim], ``<prefix>.g1`` [r', H], ``<prefix>.g2`` [heads*vdim, r'], ``<prefix>.norm`` [vdim],
@@ -44,7 +49,12 @@ class ChannelDeltaMixer(Part):
         self.hidden = int(p["hidden_size"])
         self.heads, self.kvh, self.dim, self.vdim = int(p["heads"]), int(p["kv_heads"]), int(p["dim"]), int(p["vdim"])
         self.taps = int(p["conv"])
-        self.decay_rank, self.gate_rank = int(p["decay_rank"]), int(p["gate_rank"])
+        self.head_decay = p.get("decay_per", "channel") == "head"
+        self.silu_gate = p.get("gate", "low_rank_sigmoid") == "silu"
+        if p.get("decay_per", "channel") not in ("channel", "head") or p.get("gate", "low_rank_sigmoid") not in ("low_rank_sigmoid", "silu"):
+            raise ValueError(f"{prefix}: decay_per is 'channel' or 'head', gate 'low_rank_sigmoid' or 'silu'")
+        self.decay_rank = self.heads if self.head_decay else int(p["decay_rank"])       # columns of the decay's part of the product
+        self.gate_rank = self.heads * self.vdim if self.silu_gate else int(p["gate_rank"])
         self.eps = float(p["eps"])
         if self.heads % self.kvh:
             raise ValueError(f"{prefix}: {self.heads} heads are not a multiple of {self.kvh} kv heads")
@@ -62,27 +72,34 @@ class ChannelDeltaMixer(Part):
     def tensor_specs(self):
         h, pre = self.hidden, self.prefix
         hv, hd = self.heads * self.vdim, self.heads * self.dim
-        return [TensorSpec(f"{pre}.q", (self.qk, h)), TensorSpec(f"{pre}.q.conv", (self.qk, self.taps)),
-                TensorSpec(f"{pre}.k", (self.qk, h)), TensorSpec(f"{pre}.k.conv", (self.qk, self.taps)),
-                TensorSpec(f"{pre}.v", (hv, h)), TensorSpec(f"{pre}.v.conv", (hv, self.taps)),
-                TensorSpec(f"{pre}.b", (self.heads, h)), TensorSpec(f"{pre}.A_log", (self.heads,), init="zeros"),
-                TensorSpec(f"{pre}.norm", (self.vdim,), init="ones"),
-                TensorSpec(f"{pre}.a1", (self.decay_rank, h)), TensorSpec(f"{pre}.a2", (hd, self.decay_rank)),
-                TensorSpec(f"{pre}.dt_bias", (hd,)),
-                TensorSpec(f"{pre}.g1", (self.gate_rank, h)), TensorSpec(f"{pre}.g2", (hv, self.gate_rank)),
-                TensorSpec(f"{pre}.o", (h, hv))]
+        specs = [TensorSpec(f"{pre}.q", (self.qk, h)), TensorSpec(f"{pre}.q.conv", (self.qk, self.taps)),
+                 TensorSpec(f"{pre}.k", (self.qk, h)), TensorSpec(f"{pre}.k.conv", (self.qk, self.taps)),
+                 TensorSpec(f"{pre}.v", (hv, h)), TensorSpec(f"{pre}.v.conv", (hv, self.taps)),
+                 TensorSpec(f"{pre}.b", (self.heads, h)), TensorSpec(f"{pre}.A_log", (self.heads,), init="zeros"),
+                 TensorSpec(f"{pre}.norm", (self.vdim,), init="ones"), TensorSpec(f"{pre}.o", (h, hv))]
+        if self.head_decay:
+            specs += [TensorSpec(f"{pre}.a", (self.heads, h)), TensorSpec(f"{pre}.dt_bias", (self.heads,))]
+        else:
+            specs += [TensorSpec(f"{pre}.a1", (self.decay_rank, h)), TensorSpec(f"{pre}.a2", (hd, self.decay_rank)),
+                      TensorSpec(f"{pre}.dt_bias", (hd,))]
+        if self.silu_gate:
+            specs.append(TensorSpec(f"{pre}.g", (hv, h)))
+        else:
+            specs += [TensorSpec(f"{pre}.g1", (self.gate_rank, h)), TensorSpec(f"{pre}.g2", (hv, self.gate_rank))]
+        return specs
 
     def load(self, fetch):
         pre = self.prefix
-        rows = [fetch(f"{pre}.{n}") for n in ("q", "k", "v", "b", "a1", "g1")]
+        rows = [fetch(f"{pre}.{n}") for n in ("q", "k", "v", "b", "a" if self.head_decay else "a1",
+                                              "g" if self.silu_gate else "g1")]
         dt = rows[0].dtype
         # one product for everything that reads h: [q | k | v | beta | decay's inner | gate's inner]
         self.w_in = torch.cat([t.to(dt) for t in rows], dim=0).contiguous()
         self.off_beta = self.channels
         self.off_a = self.off_beta + self.heads
         self.off_g = self.off_a + self.decay_rank
-        self.w_a2 = fetch(f"{pre}.a2").contiguous()
-        self.w_g2 = fetch(f"{pre}.g2").contiguous()
+        self.w_a2 = None if self.head_decay else fetch(f"{pre}.a2").contiguous()
+        self.w_g2 = None if self.silu_gate else fetch(f"{pre}.g2").contiguous()
         self.w_o = fetch(f"{pre}.o").contiguous()
         f32 = torch.float32
         self.conv_taps = torch.cat([fetch(f"{pre}.{n}.conv").to(f32) for n in ("q", "k", "v")], dim=0).contiguous()
@@ -94,13 +111,16 @@ class ChannelDeltaMixer(Part):
         if cache.state is None or not cache.writes:
             raise RuntimeError(f"{self.prefix}: the recurrent mixer needs a state slot of its own")
         proj = linear(normed, self.w_in)
-        a_pre = linear(proj[:, self.off_a: self.off_a + self.decay_rank], self.w_a2, out_dtype=torch.float32)
-        gate = linear(proj[:, self.off_g: self.off_g + self.gate_rank], self.w_g2)
+        a_pre = proj[:, self.off_a: self.off_a + self.decay_rank]
+        a_pre = a_pre.contiguous() if self.head_decay else linear(a_pre, self.w_a2, out_dtype=torch.float32)
+        gate = proj[:, self.off_g: self.off_g + self.gate_rank]
+        if not self.silu_gate:
+            gate = linear(gate, self.w_g2)
         q, k, v, beta, decay = ops.delta_prep(proj, 0, self.off_beta, self.conv_taps, cache.state, self.s_len, a_pre,
                                               self.dt_bias, self.a_log, ctx.cu_seqlens, ctx.seq_of_token, ctx.slots,
-                                              self.heads, self.kvh, self.dim, self.vdim)
+                                              self.heads, self.kvh, self.dim, self.vdim, head_decay=self.head_decay)
         ops.delta_conv_update(proj, 0, self.channels, self.taps, cache.state, self.s_len, ctx.cu_seqlens, ctx.slots)
         o = ops.delta_recurrence(q, k, v, beta, decay, cache.state, ctx.cu_seqlens, ctx.slots, self.heads, self.kvh,
                                  self.dim, self.vdim, general=self.GENERAL_KERNEL, single_tokens=ctx.max_new == 1)
-        y = ops.delta_out_norm(o, gate, self.w_norm, self.eps, self.vdim, proj.dtype)
+        y = ops.delta_out_norm(o, gate, self.w_norm, self.eps, self.vdim, proj.dtype, gate_silu=self.silu_gate)
         return linear(y, self.w_o)

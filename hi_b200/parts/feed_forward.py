@@ -17,22 +17,26 @@ class _SwiGLU:
     """(silu(x Wg^T) * x Wu^T) Wd^T with gate and up fused into one product
     (Mlp::forward, crates/hi-mlx/src/models.rs:2307-2312)."""
 
-    def __init__(self, prefix: str, hidden: int, inter: int):
+    def __init__(self, prefix: str, hidden: int, inter: int, short_names: bool = False):
         self.prefix, self.hidden, self.inter = prefix, hidden, inter
+        self.suffix = "" if short_names else "_proj.weight"
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
 
+    def _name(self, which: str) -> str:
+        return f"{self.prefix}.{which}{self.suffix}"
+
     def tensor_specs(self):
-        return [TensorSpec(f"{self.prefix}.gate_proj.weight", (self.inter, self.hidden)),
-                TensorSpec(f"{self.prefix}.up_proj.weight", (self.inter, self.hidden)),
-                TensorSpec(f"{self.prefix}.down_proj.weight", (self.hidden, self.inter))]
+        return [TensorSpec(self._name("gate"), (self.inter, self.hidden)),
+                TensorSpec(self._name("up"), (self.inter, self.hidden)),
+                TensorSpec(self._name("down"), (self.hidden, self.inter))]
 
     def load(self, fetch):
-        g, u = fetch(f"{self.prefix}.gate_proj.weight"), fetch(f"{self.prefix}.up_proj.weight")
+        g, u = fetch(self._name("gate")), fetch(self._name("up"))
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
         self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
-        self.w_down = fetch(f"{self.prefix}.down_proj.weight").contiguous()
+        self.w_down = fetch(self._name("down")).contiguous()
 
     def forward(self, x):
         return linear(ops.swiglu(linear(x, self.w_gate_up)), self.w_down)
@@ -40,13 +44,16 @@ class _SwiGLU:
 
 @register("feed_forward", "dense_swiglu")
 class DenseSwiGLU(Part):
-    """params: ``hidden_size``, ``intermediate_size``; tensors ``<prefix>.{gate,up,down}_proj.weight``."""
+    """W_down (silu(W_gate x) * (W_up x)).
+    params: ``hidden_size``, ``intermediate_size``, ``names`` ("proj", the default: tensors
+    ``<prefix>.{gate,up,down}_proj.weight``; "short": ``<prefix>.{gate,up,down}``)."""
 
     graph_safe = True
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
-        self.mlp = _SwiGLU(prefix, int(params["hidden_size"]), int(params["intermediate_size"]))
+        self.mlp = _SwiGLU(prefix, int(params["hidden_size"]), int(params["intermediate_size"]),
+                           short_names=params.get("names", "proj") == "short")
 
     def tensor_specs(self):
         return self.mlp.tensor_specs()

@@ -8,7 +8,7 @@ import torch
 
 from ..kernels import ops
 from .attention import attend_over_pages
-from .basic import Part
+from .basic import Part, exact_inverse_frequencies
 from .linear import linear
 from .registry import register
 from .spec import CacheSpec, TensorSpec
@@ -29,12 +29,23 @@ class LatentAttentionMixer(Part):
     A mixer with ``kv_source`` makes no latents: its schedule entry reads the cache slot of the layer that
     does (``writes_cache=False``), with its own U, V, queries and everything else.
 
-    params: ``hidden_size``, ``heads``, ``dim``, ``vdim``, ``kv_rank``, ``scale``, ``eps`` (of the latent's
-    norm), ``own_latents`` (False for a layer that reads another's), ``window`` (None | ("sliding", W) |
-    ("chunk", C): which earlier latents a query reads; default all).
-    tensors: ``<prefix>.q`` [heads*dim, H], ``<prefix>.dkv`` [rank, H] and ``<prefix>.dkv.norm`` [rank] (own
-    latents only), ``<prefix>.uk`` [heads*dim, rank], ``<prefix>.uv`` [heads*vdim, rank], ``<prefix>.g``
-    [heads, H], ``<prefix>.o`` [H, heads*vdim].
+    With ``rot_dim`` > 0 every head's query has rot_dim more dims behind its ``dim`` plain ones, and the down
+    projection rot_dim more rows behind the latent's: one key part per token that all heads share, not normed.
+    Both are rotated by the token's position (pairs (i, i + rot_dim/2), pair i by position * base^(-2i/rot_dim))
+    and the score is (q_plain . k_plain + q_rot . k_rot) * scale. The cached row is then [c | k_rot | zeros] and
+    the query in latent space [U_a^T q_plain | q_rot]: one dot product over the row gives the whole score; the
+    value map has zero rows for the key part. With ``q_rank`` the queries go through a latent of their own:
+    q = W_uq rmsnorm(W_dq h) * w_dq.
+
+    params: ``hidden_size``, ``heads``, ``dim``, ``vdim``, ``kv_rank``, ``scale``, ``eps`` (of the latents'
+    norms), ``own_latents`` (False for a layer that reads another's), ``window`` (None | ("sliding", W) |
+    ("chunk", C): which earlier latents a query reads; default all), ``gate`` (default True: the sigmoid gate
+    per head), ``q_rank`` (default None: queries straight from h), ``rot_dim`` (default 0), ``rot_base``,
+    ``rot_scaling`` (None | the keys of :func:`~hi_b200.parts.basic.exact_inverse_frequencies`).
+    tensors: ``<prefix>.q`` [heads*dim, H] (or ``<prefix>.dq`` [q_rank, H], ``<prefix>.dq.norm`` [q_rank],
+    ``<prefix>.uq`` [heads*(dim+rot_dim), q_rank]), ``<prefix>.dkv`` [rank+rot_dim, H] and ``<prefix>.dkv.norm``
+    [rank] (own latents only), ``<prefix>.uk`` [heads*dim, rank], ``<prefix>.uv`` [heads*vdim, rank],
+    ``<prefix>.g`` [heads, H] (with ``gate``), ``<prefix>.o`` [H, heads*vdim].
     """
 
     graph_safe = True
@@ -48,57 +59,94 @@ class LatentAttentionMixer(Part):
         self.eps = float(p["eps"])
         self.own = bool(p.get("own_latents", True))
         self.window = tuple(p["window"]) if p.get("window") else None
-        self.row_len = -(-self.rank // 16) * 16
+        self.gate = bool(p.get("gate", True))
+        self.q_rank = int(p["q_rank"]) if p.get("q_rank") else 0
+        self.rot = int(p.get("rot_dim") or 0)
+        if self.rot % 2:
+            raise ValueError(f"{prefix}: rot_dim {self.rot} must be even")
+        self.qdim = self.dim + self.rot                          # a query head as the checkpoint has it
+        self.row_len = -(-(self.rank + self.rot) // 16) * 16
         if self.row_len > 512:
-            raise ValueError(f"{prefix}: kv_rank {self.rank} is not supported (up to 512)")
-        self.w_in = self.w_c = self.w_uk_t = self.w_uv_t = self.w_o = None
+            raise ValueError(f"{prefix}: kv_rank {self.rank} + rot_dim {self.rot} is not supported (up to 512)")
+        self._freq_host = None
+        if self.rot:
+            self._freq_host = exact_inverse_frequencies(self.rot, float(p["rot_base"]), p.get("rot_scaling"))
+        self._freq = None
+        self.w_in = self.w_c = self.w_uk_t = self.w_uv_t = self.w_o = self.w_uq = self.w_qn = None
 
     def cache_spec(self):
         return CacheSpec(kv_heads=1, head_dim=self.row_len, window=self.window, values=False)
 
     def tensor_specs(self):
         h, hd, hv, r = self.hidden, self.heads * self.dim, self.heads * self.vdim, self.rank
-        specs = [TensorSpec(f"{self.prefix}.q", (hd, h))]
+        pre = self.prefix
+        if self.q_rank:
+            specs = [TensorSpec(f"{pre}.dq", (self.q_rank, h)), TensorSpec(f"{pre}.dq.norm", (self.q_rank,), init="ones"),
+                     TensorSpec(f"{pre}.uq", (self.heads * self.qdim, self.q_rank))]
+        else:
+            specs = [TensorSpec(f"{pre}.q", (self.heads * self.qdim, h))]
         if self.own:
-            specs += [TensorSpec(f"{self.prefix}.dkv", (r, h)), TensorSpec(f"{self.prefix}.dkv.norm", (r,), init="ones")]
-        return specs + [TensorSpec(f"{self.prefix}.uk", (hd, r)), TensorSpec(f"{self.prefix}.uv", (hv, r)),
-                        TensorSpec(f"{self.prefix}.g", (self.heads, h)), TensorSpec(f"{self.prefix}.o", (h, hv))]
+            specs += [TensorSpec(f"{pre}.dkv", (r + self.rot, h)), TensorSpec(f"{pre}.dkv.norm", (r,), init="ones")]
+        specs += [TensorSpec(f"{pre}.uk", (hd, r)), TensorSpec(f"{pre}.uv", (hv, r))]
+        if self.gate:
+            specs.append(TensorSpec(f"{pre}.g", (self.heads, h)))
+        return specs + [TensorSpec(f"{pre}.o", (h, hv))]
 
     def load(self, fetch):
-        q, g = fetch(f"{self.prefix}.q"), fetch(f"{self.prefix}.g")
-        parts = [q, g]
+        pre = self.prefix
+        q = fetch(f"{pre}.dq" if self.q_rank else f"{pre}.q")
+        parts = [q]
+        self.n_q = q.shape[0]
+        if self.gate:
+            parts.append(fetch(f"{pre}.g"))
         if self.own:
-            parts.append(fetch(f"{self.prefix}.dkv"))
-            self.w_c = fetch(f"{self.prefix}.dkv.norm").to(q.dtype).contiguous()
-        # one product for the queries, the gates and (own latents) the down projection: [q | g | dkv]
+            parts.append(fetch(f"{pre}.dkv"))
+            self.w_c = fetch(f"{pre}.dkv.norm").to(q.dtype).contiguous()
+        # one product for the queries (or their latent), the gates and (own latents) the down projection
         self.w_in = torch.cat([t.to(q.dtype) for t in parts], dim=0).contiguous()
+        if self.q_rank:
+            self.w_uq = fetch(f"{pre}.uq").to(q.dtype).contiguous()
+            self.w_qn = fetch(f"{pre}.dq.norm").to(q.dtype).contiguous()
         pad = self.row_len - self.rank
-        uk = fetch(f"{self.prefix}.uk").view(self.heads, self.dim, self.rank)
-        uv = fetch(f"{self.prefix}.uv").view(self.heads, self.vdim, self.rank)
+        uk = fetch(f"{pre}.uk").view(self.heads, self.dim, self.rank)
+        uv = fetch(f"{pre}.uv").view(self.heads, self.vdim, self.rank)
         if pad:
             uk = torch.nn.functional.pad(uk, (0, pad))
             uv = torch.nn.functional.pad(uv, (0, pad))
         self.w_uk = uk.contiguous()                              # [heads, dim, row_len]: q_a -> latent space
         self.w_uv_t = uv.transpose(1, 2).contiguous()            # [heads, row_len, vdim]: latent space -> o_a
-        self.w_o = fetch(f"{self.prefix}.o").contiguous()
+        self.w_o = fetch(f"{pre}.o").contiguous()
+        if self.rot:
+            self._freq = torch.from_numpy(self._freq_host).to(self.w_in.device)
 
     def forward(self, normed, ctx, cache):
-        n, hd = normed.shape[0], self.heads * self.dim
+        n = normed.shape[0]
         proj = linear(normed, self.w_in)
         block_table = ctx.block_tables[cache.group]
         if self.own != cache.writes:
             raise RuntimeError(f"{self.prefix}: a layer with its own latents writes its cache slot, another reads one")
+        off_g = self.n_q
+        off_kv = off_g + (self.heads if self.gate else 0)
         if self.own:
-            ops.latent_append(proj[:, hd + self.heads:], self.w_c, self.eps, ctx.positions, ctx.seq_of_token, block_table,
-                              cache.k_pages)
+            ops.latent_append(proj[:, off_kv:], self.w_c, self.eps, ctx.positions, ctx.seq_of_token, block_table,
+                              cache.k_pages, inv_freq=self._freq)
+        if self.q_rank:
+            q = linear(ops.rmsnorm_rows(proj[:, : self.q_rank], self.w_qn, self.eps), self.w_uq)
+        else:
+            q = proj[:, : self.n_q]
+        q = q.view(n, self.heads, self.qdim) if q.is_contiguous() else q.reshape(n, self.heads, self.qdim)
         # queries into latent space, head by head: [heads, N, dim] x [heads, dim, row_len]
         q_lat = torch.empty((n, self.heads, self.row_len), dtype=proj.dtype, device=proj.device)
-        torch.bmm(proj[:, :hd].view(n, self.heads, self.dim).transpose(0, 1), self.w_uk, out=q_lat.transpose(0, 1))
+        torch.bmm(q[:, :, : self.dim].transpose(0, 1), self.w_uk, out=q_lat.transpose(0, 1))
+        if self.rot:
+            # the rotated part of every head's query, turned by the token's position, behind its latent part
+            ops.rope_copy(q[:, :, self.dim:], q_lat[:, :, self.rank: self.rank + self.rot], ctx.positions, self._freq)
         chunk = self.window[1] if self.window and self.window[0] == "chunk" else 0
         sliding = self.window[1] if self.window and self.window[0] == "sliding" else 0
         o_lat = attend_over_pages(q_lat, cache.k_pages, cache.k_pages, block_table, ctx, self.heads, 1, self.row_len,
                                   chunk, sliding, self.scale)
         o = torch.empty((n, self.heads, self.vdim), dtype=proj.dtype, device=proj.device)
         torch.bmm(o_lat.transpose(0, 1), self.w_uv_t, out=o.transpose(0, 1))
-        o = ops.head_gate(o, proj[:, hd: hd + self.heads])
+        if self.gate:
+            o = ops.head_gate(o, proj[:, off_g: off_g + self.heads])
         return linear(o.view(n, self.heads * self.vdim), self.w_o)

@@ -9,8 +9,10 @@ from . import attention as _attention  # noqa: F401  (registers the parts)
 from . import basic as _basic          # noqa: F401
 from . import delta_rule as _delta     # noqa: F401
 from . import feed_forward as _ffn     # noqa: F401
+from . import gla as _gla              # noqa: F401
 from . import latent_attention as _latent  # noqa: F401
 from . import mlstm as _mlstm          # noqa: F401
+from . import pair as _pair            # noqa: F401
 from .context import CacheView, StepContext
 from .registry import BuildEnv, build
 from .spec import CacheSpec, ModelSpec, PartSpec, TensorSpec
@@ -51,9 +53,12 @@ class Model:
         self.layers = [Layer(ls, self.env) for ls in spec.layers]
         self.final_norm = build("norm", spec.final_norm, self.env, spec.final_norm.params.get("name", ""))
         self.head = build("head", spec.head, self.env, spec.head.params.get("name", ""))
+        self.interludes = [build("interlude", ps, self.env, ps.params.get("name", "")) for ps in spec.interludes]
         for i, entry in enumerate(spec.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"schedule entry {i} names layer {entry.layer}; the model has {len(self.layers)}")
+            if entry.interlude is not None and not 0 <= entry.interlude < len(self.interludes):
+                raise ValueError(f"schedule entry {i} names interlude {entry.interlude}; the model has {len(self.interludes)}")
         # cache slots: the spec of the mixer of the first entry that names the slot
         self.cache_specs: Dict[int, Optional[CacheSpec]] = {}
         for entry in spec.schedule:
@@ -63,6 +68,12 @@ class Model:
                     raise ValueError(f"cache slot {entry.cache} is shared by mixers with different cache needs")
             else:
                 self.cache_specs[entry.cache] = cs
+        # fixed-size state of a block arrangement (what its layer keeps per request beside the mixer's), by cache slot
+        self.block_state_sizes: Dict[int, int] = {}
+        for entry in spec.schedule:
+            size = int(self.layers[entry.layer].arrangement.state_size())
+            if size and entry.writes_cache:
+                self.block_state_sizes[entry.cache] = size
         writers = {e.cache for e in spec.schedule if e.writes_cache}
         for slot in self.cache_specs:
             if slot not in writers:
@@ -75,7 +86,7 @@ class Model:
         parts = [self.embedding]
         for layer in self.layers:
             parts += layer.parts()
-        return parts + [self.final_norm, self.head]
+        return parts + self.interludes + [self.final_norm, self.head]
 
     def tensor_specs(self) -> List[TensorSpec]:
         specs: List[TensorSpec] = []
@@ -96,13 +107,17 @@ class Model:
             raise RuntimeError("model weights are not loaded")
         ctx.scratch = {}
         residual = self.embedding.forward(ctx.tokens)
+        if any(getattr(p, "needs_embedding_output", False) for p in self.interludes):
+            ctx.scratch["embedding_output"] = residual.clone()       # the stream is summed into in place
         pending = None
         for entry in self.spec.schedule:
             layer = self.layers[entry.layer]
             view = caches[entry.cache]
             if view.writes != entry.writes_cache:
                 view = CacheView(group=view.group, k_pages=view.k_pages, v_pages=view.v_pages, state=view.state,
-                                 writes=entry.writes_cache, slot=view.slot)
+                                 writes=entry.writes_cache, slot=view.slot, block_state=view.block_state)
+            if entry.interlude is not None:
+                residual, pending = self.interludes[entry.interlude].forward(residual, pending, ctx, entry.interlude_arg)
             residual, pending = layer.arrangement.forward(layer, residual, pending, ctx, view)
         if logit_rows is None or logit_rows.numel() == 0:
             return None

@@ -14,6 +14,9 @@ Families and the interface each member must have (all also have
 ``arrangement``   ``forward(layer, residual, pending, ctx, cache_view) -> (residual, pending)``.
 ``embedding``     ``forward(tokens_i32) -> residual_f32``; ``table`` for a tied head.
 ``head``          ``forward(normed_rows) -> logits_f32``.
+``interlude``     ``forward(residual, pending, ctx, arg) -> (residual, pending)``: acts on the stream between
+                  two runs of layers; ``needs_embedding_output`` asks the model to keep a copy of the
+                  embedding output in ``ctx.scratch["embedding_output"]``.
 """
 from __future__ import annotations
 
@@ -24,7 +27,7 @@ import torch
 
 from .spec import PartSpec
 
-FAMILIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head")
+FAMILIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head", "interlude")
 _REGISTRY: Dict[str, Dict[str, Callable[..., Any]]] = {f: {} for f in FAMILIES}
 
 

@@ -91,11 +91,16 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer. ``cache`` names the cache slot its mixer uses; two entries
-    with the same ``cache`` share it, and only entries with ``writes_cache`` append."""
+    with the same ``cache`` share it, and only entries with ``writes_cache`` append.
+    ``interlude``: index into ``ModelSpec.interludes`` of a part that acts on the stream right before
+    this run (what a model adds between two passes over a range of its layers), with ``interlude_arg``
+    (the number of the pass)."""
 
     layer: int
     cache: int
     writes_cache: bool = True
+    interlude: Optional[int] = None
+    interlude_arg: int = 0
 
 
 @dataclass(frozen=True)
@@ -109,6 +114,7 @@ class ModelSpec:
     head: PartSpec
     eos_token_ids: Tuple[int, ...] = ()
     max_position_embeddings: Optional[int] = None
+    interludes: Tuple[PartSpec, ...] = ()
 
     @staticmethod
     def sequential(n_layers: int) -> Tuple[ScheduleEntry, ...]:
