@@ -814,11 +814,12 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
 def sigmoid_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                       seq_of_token: torch.Tensor, positions: torch.Tensor, chunk: int, window: int, scale: float,
                       head_bias: Optional[torch.Tensor], max_context: int = 0,
-                      v_inv_freq: Optional[torch.Tensor] = None, v_interleaved: bool = False) -> torch.Tensor:
+                      v_inv_freq: Optional[torch.Tensor] = None, v_interleaved: bool = False,
+                      split_size: Optional[int] = None) -> torch.Tensor:
     """sum_j sigmoid(q . k_j * scale + head_bias[h]) v_j over the keys each token may read (no normalisation);
     q [N, nh, hd] -> [N, nh, hd]. With ``v_inv_freq`` the cached values are taken as rotated by their positions
     and every head's sum is turned back by the query's position (see :func:`qkv_post`). Long ranges are cut into
-    splits of ``ATTENTION_SPLIT`` keys as in :func:`paged_attention`; the splits add."""
+    splits of ``split_size`` keys (default ``ATTENTION_SPLIT``) as in :func:`paged_attention`; the splits add."""
     _need(q, "q"); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
     for t, nm in ((block_table, "block_table"), (seq_of_token, "seq_of_token"), (positions, "positions")):
         _need(t, nm, torch.int32)
@@ -842,12 +843,13 @@ def sigmoid_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         longest = min(longest, chunk)
     if window > 0:
         longest = min(longest, window)
-    splits = max(1, -(-longest // ATTENTION_SPLIT))
+    split_size = int(split_size or ATTENTION_SPLIT)
+    splits = max(1, -(-longest // split_size))
     part_acc = torch.empty((n, nh, splits, hd), dtype=torch.float32, device=q.device) if splits > 1 else None
     _check(lib().hb_sigmoid_attention(_ptr(q), _dt(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                                       block_table.shape[1], _ptr(seq_of_token), _ptr(positions), _ptr(head_bias),
                                       _ptr(v_inv_freq), v_pairs, int(v_interleaved), _ptr(out), n, nh, nkv, hd,
-                                      page_size, int(chunk), int(window), float(scale), ATTENTION_SPLIT, splits,
+                                      page_size, int(chunk), int(window), float(scale), split_size, splits,
                                       _ptr(part_acc), _stream()), "sigmoid_attention")
     return out
 

@@ -32,7 +32,8 @@ class Layer:
         self.mixer = build("mixer", spec.mixer, env, sub(spec.mixer))
         self.norm_feed_forward = self.feed_forward = None
         if spec.feed_forward is not None:
-            self.norm_feed_forward = build("norm", spec.norm_feed_forward, env, sub(spec.norm_feed_forward))
+            if spec.norm_feed_forward is not None:       # None: the block's two sub-layers share one norm
+                self.norm_feed_forward = build("norm", spec.norm_feed_forward, env, sub(spec.norm_feed_forward))
             self.feed_forward = build("feed_forward", spec.feed_forward, env, sub(spec.feed_forward))
         arrangement = spec.arrangement if isinstance(spec.arrangement, PartSpec) else PartSpec(spec.arrangement)
         self.arrangement = build("arrangement", arrangement, env, spec.prefix)

@@ -58,7 +58,7 @@ def build_surinex_spec(cfg: SurinexConfig) -> ModelSpec:
                                                                  "intermediate_size": l.ff, "names": "short"})
         norm = PartSpec("rmsnorm", {"name": "norm1", "size": w, "eps": cfg.eps, "tensor": "bare"})
         layers.append(LayerSpec(prefix=f"l{i}", mixer=_mixer(cfg, l), feed_forward=ffn, norm_mixer=norm,
-                                norm_feed_forward=None if ffn is None else norm,
+                                norm_feed_forward=None,
                                 arrangement=PartSpec("parallel_conv", {"hidden_size": w, "taps": cfg.taps,
                                                                        "feed_forward": ffn is not None})))
     n = len(layers)
