@@ -969,6 +969,221 @@ def case_delta_recurrence(tokens=2048, heads=16, seqs=1):
         torch.cuda.synchronize()
         print(f"{rows} rows a lane: {a.elapsed_time(b) * 1e3:.1f} us")
 
+# --------------------------------------------------------------------------- Surinex beside the closest existing models
+def _surinex_config(width, heads, ff, layers, vocab=32000, passes=2):
+    """Layers in the order gla, pair (sigmoid attention beside the delta rule), latent attention, gla, ...; head sizes
+    128 (the latent row is 128 + 64 rotated); the first two layers run ``passes`` times."""
+    mlp = {"kind": "dense", "ff": ff}
+    gla = {"type": "gla", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 64}, "mlp": mlp}
+    pair = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+        "right": {"heads": heads // 2, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "conv": 4}}}
+    latent = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 128, "q_rank": width // 2, "scale": 192 ** -0.5,
+        "rot": {"base": 500000.0, "dims": 64}}}
+    order = [(gla, pair, latent)[i % 3] for i in range(layers)]
+    return {"architecture": "Surinex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+            "layers": order, "loop": {"start": 0, "stop": min(2, layers), "times": passes}}
+
+
+def case_surinex(width=2048, heads=16, ff=8192, layers=6, tokens=2048, batch=8, context=4096):
+    """Prefill (one prompt of ``tokens`` in one step) and decode (``batch`` requests at ``context`` cached tokens,
+    captured steps) throughput of a Surinex model with random weights beside Vinurax (the closest existing model:
+    latent attention and a delta rule in side-by-side blocks) and a dense Llama-4-shaped model of equal width,
+    depth, heads and feed-forward size; then the new kernels alone beside their like kernels, with the bytes that
+    must move over the measured copy bandwidth. Markdown on standard output."""
+    import torch
+
+    from hi_b200.engine.core import Engine, StepEntry
+    from hi_b200.kernels import ops
+
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    g = torch.Generator().manual_seed(0)
+
+    def timed(fn, reps=5, flush_l2=True):
+        fn()
+        ts = []
+        for _ in range(reps):
+            if flush_l2:
+                flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2]
+
+    print(f"peaks: {pk['hbm_gbs']:.0f} GB/s copy, {pk['bf16_tflops']:.0f} TFLOP/s bf16 ({pk['source']}); "
+          f"width {width}, {heads} heads of 128, feed-forward {ff}, {layers} layers, bf16, random weights\n")
+    print("| model | layer runs | prefill tokens/s | ms | decode tokens/s | ms/step | weights GB | launches/decode step |\n|---|---|---|---|---|---|---|---|")
+    for name, cfg in (("Surinex", _surinex_config(width, heads, ff, layers)), ("Vinurax", _vinurax_config(width, heads, ff, layers)),
+                      ("dense Llama-4 shape", _dense_llama_config(width, heads, ff, layers))):
+        eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", device=DEV, kv_page_size=PAGE,
+                                 kv_cache_tokens=batch * (context + 256) + tokens + 256, max_active_requests=batch + 1)
+        vocab = eng.vocab_size
+        weights = sum(2 * int(torch.Size(sp.shape).numel()) for sp in eng.model.tensor_specs() if sp.init != "absent") / 1e9
+        prompt = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+
+        def prefill():
+            eng.step([StepEntry("p", prompt, [tokens - 1])])
+            eng.finish("p")
+        t_pre = timed(prefill, reps=3)
+        for i in range(batch):
+            eng.assume_cached(i, context)
+        toks = torch.randint(0, vocab, (64, batch), generator=g).tolist()
+        turn = [0]
+
+        def decode():
+            eng.step([StepEntry(i, [toks[turn[0] % 64][i]], [0]) for i in range(batch)], borrow=True)
+            turn[0] += 1
+        for _ in range(4):
+            decode()
+        before = ops.LAUNCHES[0]
+        t_dec = timed(decode, reps=9, flush_l2=False)
+        launches = (ops.LAUNCHES[0] - before) // 10
+        print(f"| {name} | {len(eng.model.spec.schedule)} | {tokens / t_pre * 1e3:,.0f} | {t_pre:.2f} | {batch / t_dec * 1e3:,.0f} | "
+              f"{t_dec:.3f} | {weights:.2f} | {launches} |")
+        del eng
+        torch.cuda.empty_cache()
+
+    # ---- kernels alone: bytes that must move over the time, against the copy peak
+    bf, f32 = torch.bfloat16, torch.float32
+    dg = torch.Generator(device=DEV).manual_seed(0)
+    rnd = lambda *shape, dt=bf: torch.randn(*shape, device=DEV, generator=dg).to(dt)
+    rows = []
+
+    def row(kind, name, ms, nbytes, note=""):
+        rows.append(f"| {kind} | {name} | {ms * 1e3:.1f} | {nbytes / 1e6:.1f} | {nbytes / ms / 1e6:,.0f} | "
+                    f"{nbytes / ms / 1e6 / pk['hbm_gbs']:.2f} | {note} |")
+
+    hd = heads * 128
+    nkv = max(1, heads // 4)
+    for n, seqs, what in ((tokens, 1, "prefill"), (batch, batch, "decode")):
+        cu = torch.arange(0, n + 1, n // seqs, dtype=torch.int32, device=DEV)
+        sot = torch.repeat_interleave(torch.arange(seqs, device=DEV), n // seqs).to(torch.int32)
+        slots = torch.arange(seqs, dtype=torch.int32, device=DEV)
+        # the block: norm, the two convolutions, the sum between passes, the mean of two mixers
+        x, h = rnd(n, width, dt=f32), rnd(n, width, dt=f32)
+        d1, d2, w = rnd(n, width), rnd(n, width), rnd(width)
+        ta, tb = rnd(width, 4, dt=f32), rnd(width, 4, dt=f32)
+        cstate = torch.zeros(seqs, 3 * width, device=DEV)
+        ms = timed(lambda: ops.add_rmsnorm(x, d1, w, 1e-5, f32, delta2=d2))
+        row(what, "residual add of two results + RMSNorm, float32 out", ms, n * width * (4 + 2 + 2 + 4 + 4))
+        ms = timed(lambda: ops.add_rmsnorm(x, d1, w, 1e-5, bf))
+        row(what, "like: residual add + RMSNorm", ms, n * width * (4 + 2 + 4 + 2), "twice per layer there")
+        ms = timed(lambda: ops.canon_conv(h, ta, tb, cstate, cu, sot, slots, bf))
+        row(what, "two convolutions of the norm's output (4 taps) + state", ms, n * width * (4 + 2 + 2), "two launches")
+        emb, vec = rnd(n, width, dt=f32), rnd(width, dt=f32)
+        ms = timed(lambda: ops.stream_add(x, d1, d2, emb, vec))
+        row(what, "between passes: stream += two results + embedding + vector", ms, n * width * (4 + 2 + 2 + 4 + 4))
+        ms = timed(lambda: ops.rmsnorm_mean2(d1, d2, w, w, 1e-5, bf))
+        row(what, "mean of two RMS-normed mixer outputs", ms, n * width * 6)
+        # gated linear attention
+        proj, z, bias = rnd(n, 4 * hd + 64), rnd(n, hd, dt=f32), rnd(hd, dt=f32)
+        ms = timed(lambda: ops.gla_prep(proj, 0, hd, 2 * hd, z, bias, 16.0, 128 ** -0.5, hd, hd))
+        row(what, "gla: q, k, v to float32, decay", ms, n * hd * (3 * 2 + 4 + 4 * 4))
+        q, k, v, decay = ops.gla_prep(proj, 0, hd, 2 * hd, z, bias, 16.0, 128 ** -0.5, hd, hd)
+        k = torch.nn.functional.normalize(k.view(n, heads, 128), dim=-1).view(n, hd).contiguous()
+        s_len = heads * 128 * 128
+        state = torch.zeros(seqs, s_len, device=DEV)
+        ms = timed(lambda: ops.delta_recurrence(q, k, v, None, decay, state, cu, slots, heads, heads, 128, 128,
+                                                single_tokens=seqs == n, plain=True))
+        row(what, "gla: recurrence", ms, n * 4 * hd * 4 + n * hd * 4 + 2 * seqs * s_len * 4,
+            f"{n * heads * 128 * 128 * 2 * 2 / ms / 1e9:,.1f} TFLOP/s float32 of its own arithmetic")
+        beta = torch.rand(n, heads, device=DEV)
+        state.zero_()
+        ms = timed(lambda: ops.delta_recurrence(q, k, v, beta, decay, state, cu, slots, heads, heads, 128, 128,
+                                                single_tokens=seqs == n))
+        row(what, "like: delta rule recurrence", ms, n * 4 * hd * 4 + n * (hd + heads) * 4 + 2 * seqs * s_len * 4,
+            f"{n * heads * 128 * 128 * 2 * 3 / ms / 1e9:,.1f} TFLOP/s float32 of its own arithmetic")
+        o, wn = rnd(n, hd, dt=f32), rnd(128)
+        ms = timed(lambda: ops.delta_out_norm(o, proj[:, 3 * hd: 4 * hd], wn, 1e-5, 128, bf, gate_silu=True))
+        row(what, "gla / delta rule: output norm and silu gate", ms, n * hd * (4 + 2 + 2))
+    # attention: encoding and the kernels themselves, a prompt of `tokens` and `batch` single tokens at `context`
+    for n, seqs, ctx_len, what in ((tokens, 1, tokens, "prefill"), (batch, batch, context, "decode")):
+        per = -(-ctx_len // PAGE)
+        pages = seqs * per
+        pos = (torch.arange(n, device=DEV) if seqs == 1 else torch.full((n,), ctx_len - 1, device=DEV)).to(torch.int32)
+        sot = torch.repeat_interleave(torch.arange(seqs, device=DEV), n // seqs).to(torch.int32)
+        cu = torch.arange(0, n + 1, n // seqs, dtype=torch.int32, device=DEV)
+        table = torch.randperm(pages, device=DEV, generator=dg).to(torch.int32).view(seqs, per).contiguous()
+        qkv = rnd(n, (heads + 2 * nkv) * 128)
+        kp, vp = rnd(pages, nkv, PAGE, 128), rnd(pages, nkv, PAGE, 128)
+        inv = torch.tensor([500000.0 ** (-2.0 * i / 64) for i in range(32)], device=DEV)
+        vinv = torch.tensor([500000.0 ** (-2.0 * i / 128) for i in range(64)], device=DEV)
+        wq = torch.ones(128, device=DEV)
+        ms = timed(lambda: ops.qkv_post(qkv, heads, nkv, 128, pos, inv, True, True, 1e-5, None, sot, table, kp, vp, PAGE, True,
+                                        q_norm_weight=wq, k_norm_weight=wq, norm_first=True, norm_dim=128, v_inv_freq=vinv,
+                                        v_interleaved=True))
+        row(what, "sigmoid attention: weighted q/k norm, rotation, rotated values, append", ms, n * (heads + 2 * nkv) * 128 * 4)
+        ms = timed(lambda: ops.qkv_post(qkv, heads, nkv, 128, pos, inv, True, True, 1e-5, None, sot, table, kp, vp, PAGE, True,
+                                        q_norm_weight=wq, k_norm_weight=wq, norm_first=True, norm_dim=128))
+        row(what, "like: the same without rotated values (Fidatar's encoding)", ms, n * (heads + 2 * nkv) * 128 * 4)
+        q = rnd(n, heads, 128)
+        pb = rnd(heads, dt=f32) - 4.0
+        pairs = n * (n + 1) // 2 if seqs == 1 else n * ctx_len
+        kv_bytes = (ctx_len if seqs == 1 else n * ctx_len) * nkv * 128 * 2 * 2 + n * heads * 128 * 4
+        ms = timed(lambda: ops.sigmoid_attention(q, kp, vp, table, sot, pos, 0, 0, 128 ** -0.5, pb, ctx_len, v_inv_freq=vinv,
+                                                 v_interleaved=True))
+        row(what, "sigmoid attention over pages, general kernel (float32, other head sizes)", ms, kv_bytes,
+            f"{pairs * heads * 128 * 4 / ms / 1e9:,.1f} TFLOP/s")
+        if seqs == 1:
+            ms = timed(lambda: ops.sigmoid_prefill_attention_tc(q, kp, vp, table, cu, pos, 1, n, 0, 0, 128 ** -0.5, pb,
+                                                                v_inv_freq=vinv, v_interleaved=True))
+            row(what, "sigmoid attention, tcgen05 prefill + turn back", ms, kv_bytes, f"{pairs * heads * 128 * 4 / ms / 1e9:,.1f} TFLOP/s")
+            ms = timed(lambda: ops.prefill_attention_tc(q, kp, vp, table, cu, pos, 1, n, 0, 0, 128 ** -0.5))
+            row(what, "like: softmax attention, tcgen05 prefill", ms, kv_bytes, f"{pairs * heads * 128 * 4 / ms / 1e9:,.1f} TFLOP/s")
+        else:
+            ms = timed(lambda: ops.sigmoid_decode_attention(q, kp, vp, table, sot, pos, 0, 0, 128 ** -0.5, pb, ctx_len, vinv, True))
+            row(what, "sigmoid attention, decode kernel + turn back", ms, kv_bytes)
+            ms = timed(lambda: ops.decode_attention(q, kp, vp, table, sot, pos, 0, 0, 128 ** -0.5, ctx_len))
+            row(what, "like: softmax attention, decode kernel", ms, kv_bytes)
+        # latent rows
+        lat, wl = rnd(n, 128 + 64 + 32), rnd(128)
+        pool = torch.zeros(pages, 1, PAGE, 192, dtype=bf, device=DEV)
+        ms = timed(lambda: ops.latent_append(lat[:, 32:], wl, 1e-5, pos, sot, table, pool, inv_freq=inv))
+        row(what, "latent: RMS norm + rotated key part into its page (128 + 64)", ms, n * 192 * 4)
+        pool2 = torch.zeros(pages, 1, PAGE, 128, dtype=bf, device=DEV)
+        ms = timed(lambda: ops.latent_append(lat[:, 32: 160], wl, 1e-5, pos, sot, table, pool2))
+        row(what, "like: latent RMS norm into its page (128)", ms, n * 128 * 4)
+        ql = rnd(n, heads, 192)
+        ms = timed(lambda: ops.paged_attention(ql, pool, pool, table, sot, pos, 0, 0, 192 ** -0.5, ctx_len))
+        lat_bytes = (ctx_len if seqs == 1 else n * ctx_len) * 192 * 2 + n * heads * 192 * 4
+        row(what, "latent attention over rows of 192 (general kernel)", ms, lat_bytes, f"{pairs * heads * 192 * 4 / ms / 1e9:,.1f} TFLOP/s")
+        ql2 = rnd(n, heads, 128)
+        if seqs == 1:
+            ms = timed(lambda: ops.prefill_attention_tc(ql2, pool2, pool2, table, cu, pos, 1, n, 0, 0, 128 ** -0.5))
+        else:
+            ms = timed(lambda: ops.decode_attention(ql2, pool2, pool2, table, sot, pos, 0, 0, 128 ** -0.5, ctx_len))
+        row(what, "like: Vinurax's latent attention over rows of 128 (tensor-core kernel)", ms,
+            (ctx_len if seqs == 1 else n * ctx_len) * 128 * 2 + n * heads * 128 * 4, f"{pairs * heads * 128 * 4 / ms / 1e9:,.1f} TFLOP/s")
+    ops.check_tc_status()
+    print("\n| step | kernel | us | MB that must move | GB/s | of the copy peak | |\n|---|---|---|---|---|---|---|")
+    print("\n".join(rows))
+
+
+def case_surinex_step(tokens=2048, batch=8, context=4096, width=2048, heads=16, ff=8192, layers=3):
+    """One Surinex prompt step and two decode steps with every kernel launched on its own (no captured graph),
+    three layers (gla, pair, latent attention; the first two run twice): for a launch list under ncu."""
+    import torch
+
+    from hi_b200.engine.core import Engine, StepEntry
+
+    eng = Engine.from_config(_surinex_config(width, heads, ff, layers), seed=0, dtype="bfloat16", device=DEV, kv_page_size=PAGE,
+                             kv_cache_tokens=batch * (context + 256) + tokens + 256, max_active_requests=batch + 1,
+                             use_cuda_graphs=False)
+    g = torch.Generator().manual_seed(0)
+    for rep in range(2):
+        eng.step([StepEntry("p", torch.randint(0, eng.vocab_size, (tokens,), generator=g).tolist(), [tokens - 1])])
+        eng.finish("p")
+    for i in range(batch):
+        eng.assume_cached(i, context)
+    for _ in range(3):
+        eng.step([StepEntry(i, [int(torch.randint(0, eng.vocab_size, (1,), generator=g))], [0]) for i in range(batch)])
+    torch.cuda.synchronize()
+
+
 # --------------------------------------------------------------------------- Fidatar beside the closest existing models
 def _fidatar_config(width, heads, ff, layers, vocab=32000, chunk=8192):
     """Layers in turn attention (heads of 128, a quarter as many key heads, chunks of 8,192, half of a head
@@ -1298,7 +1513,7 @@ CASES = {"sweep": case_sweep, "decode_timeline": case_decode_timeline, "prefill_
          "prefill_attention": case_prefill_attention, "decode_step": case_decode_step, "prefill_step": case_prefill_step,
          "vinurax": case_vinurax, "delta_recurrence": case_delta_recurrence,
          "vinurax_step": case_vinurax_step, "fidatar": case_fidatar, "fidatar_step": case_fidatar_step,
-         "mlstm_recurrence": case_mlstm_recurrence}
+         "mlstm_recurrence": case_mlstm_recurrence, "surinex": case_surinex, "surinex_step": case_surinex_step}
 
 
 if __name__ == "__main__":

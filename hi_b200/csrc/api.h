@@ -49,7 +49,8 @@ int hb_attention_merge(const float* part_acc, const float* part_ml, void* out, i
 int hb_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                         int table_stride, const int* seq_of_token, const int* positions, void* out, int n_tokens,
                         int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int sink,
-                        int split_size, int max_splits, float* part_acc, float* part_ml, cudaStream_t stream);
+                        const float* head_bias, int split_size, int max_splits, float* part_acc, float* part_ml,
+                        cudaStream_t stream);   // sink == 2: sigmoid weights with head_bias; plain sums go to part_acc
 
 int hb_attention_decode_tma(const void* q, const void* k_pages, const void* v_pages, int n_pages, const int* block_table,
                             int table_stride, const int* seq_of_token, const int* positions, void* out, int n_tokens,
@@ -75,8 +76,8 @@ int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages
 int hb_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                             int table_stride, const int* cu_seqlens, const int* positions, void* out, int n_tokens,
                             int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd, int page_size, int chunk,
-                            int window, float scale, int skip_single, int sink, int key_splits, float* part_acc,
-                            float* part_ml, int* status, cudaStream_t stream);
+                            int window, float scale, int skip_single, int sink, const float* head_bias, int key_splits,
+                            float* part_acc, float* part_ml, int* status, cudaStream_t stream);   // sink == 2 as above
 
 // mode: bit 0 = scores are the softmax over all experts (clear: the sigmoid of the chosen logit),
 // bit 1 = the chosen scores are divided by their sum; bits 8-15 = G, 16-23 = KEEP: only experts of the KEEP best
@@ -193,6 +194,11 @@ int hb_sigmoid_attention(const void* q, int dtype, const void* k_pages, const vo
                          const float* v_inv_freq, int v_pairs, int v_interleaved, void* out, int n_tokens, int nh,
                          int nkv, int hd, int page_size, int chunk, int window, float scale, int split_size,
                          int max_splits, float* part_acc, cudaStream_t stream);
+
+// the splits of every (token, head) of part_acc [n_tokens * nh][max_splits][hd] added in split order and turned back
+int hb_sigmoid_merge(const float* part_acc, const int* positions, const float* v_inv_freq, int v_pairs,
+                     int v_interleaved, void* out, int dtype, int n_tokens, int nh, int hd, int max_splits,
+                     cudaStream_t stream);
 
 #ifdef __cplusplus
 }

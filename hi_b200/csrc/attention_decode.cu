@@ -55,8 +55,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table,
                    int table_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                    __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int chunk, int window,
-                   float scale, int sink, int split_size, int max_splits, float* __restrict__ part_acc,
-                   float* __restrict__ part_ml) {
+                   float scale, int sink, const float* __restrict__ head_bias, int split_size, int max_splits,
+                   float* __restrict__ part_acc, float* __restrict__ part_ml) {
+  // sink == 2: sigmoid weights. The weight of a key is sigmoid(score + head_bias[head]), nothing is normalised,
+  // and every split's plain sum goes to part_acc (also when there is one split): the caller adds the splits.
+  const bool sigmoid = sink == 2;
   constexpr int STRIDE = HD + 8;                 // padded row: ldmatrix without bank conflicts
   constexpr int CHUNKS = HD / 8;                 // 16-byte chunks per row
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -77,7 +80,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int first = lo + split * split_size;
   const size_t th0 = (size_t)t * nh + (size_t)kvh * G;      // (token, first head of the group)
   if (first > pos) {                                          // this token has fewer splits
-    if (max_splits > 1 && tid < G) {
+    if (sigmoid) {
+      for (int i = tid; i < G * HD; i += NWARPS * 32)
+        part_acc[((th0 + i / HD) * max_splits + split) * HD + i % HD] = 0.f;
+    } else if (max_splits > 1 && tid < G) {
       float* ml = part_ml + ((th0 + tid) * max_splits + split) * 2;
       ml[0] = -INFINITY; ml[1] = 0.f;
     }
@@ -139,6 +145,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
     for (int e = 0; e < 4; ++e) o_acc[j][e] = 0.f;
   unsigned q_frag[HD / 16][4];
+  float row_bias[2] = {0.f, 0.f};
+  if (sigmoid && head_bias) {
+    if (lane / 4 < G) row_bias[0] = head_bias[kvh * G + lane / 4];
+    if (lane / 4 + 8 < G) row_bias[1] = head_bias[kvh * G + lane / 4 + 8];
+  }
 
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int buf = tile & 1;
@@ -168,56 +179,71 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     }
     // scale, mask keys past the split's end, online softmax per row (rows lane/4 and lane/4 + 8)
     const int key0 = first + tile * TILE + warp * 16 + (lane % 4) * 2;
-    float tile_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = key0 + nt * 8 + (e & 1);
-        const float v = key <= last ? s_acc[nt][e] * scale : -INFINITY;
-        s_acc[nt][e] = v;
-        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
-      }
-    float corr[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      float mx = tile_max[r];
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float m_new = fmaxf(m_run[r], mx);
-      corr[r] = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - m_new);
-      m_run[r] = m_new;
-    }
-    float row_sum[2] = {0.f, 0.f};
     unsigned p_frag[4];
-    {
+    if (sigmoid) {
       float p[2][4];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int r = e >> 1;
-          const float v = (s_acc[nt][e] == -INFINITY) ? 0.f : __expf(s_acc[nt][e] - m_run[r]);
-          p[nt][e] = v;
-          row_sum[r] += v;
+          const int key = key0 + nt * 8 + (e & 1);
+          p[nt][e] = key <= last ? 1.f / (1.f + __expf(-(s_acc[nt][e] * scale + row_bias[e >> 1]))) : 0.f;
         }
       p_frag[0] = pack_bf16(p[0][0], p[0][1]);
       p_frag[1] = pack_bf16(p[0][2], p[0][3]);
       p_frag[2] = pack_bf16(p[1][0], p[1][1]);
       p_frag[3] = pack_bf16(p[1][2], p[1][3]);
-    }
+    } else {
+      float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      float sum = row_sum[r];
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      l_run[r] = l_run[r] * corr[r] + sum;
-    }
-    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // the running max rarely moves
+      for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int j = 0; j < HD / 8; ++j) {
-        o_acc[j][0] *= corr[0]; o_acc[j][1] *= corr[0];
-        o_acc[j][2] *= corr[1]; o_acc[j][3] *= corr[1];
+        for (int e = 0; e < 4; ++e) {
+          const int key = key0 + nt * 8 + (e & 1);
+          const float v = key <= last ? s_acc[nt][e] * scale : -INFINITY;
+          s_acc[nt][e] = v;
+          tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+        }
+      float corr[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float mx = tile_max[r];
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[r], mx);
+        corr[r] = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - m_new);
+        m_run[r] = m_new;
+      }
+      float row_sum[2] = {0.f, 0.f};
+      {
+        float p[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const float v = (s_acc[nt][e] == -INFINITY) ? 0.f : __expf(s_acc[nt][e] - m_run[r]);
+            p[nt][e] = v;
+            row_sum[r] += v;
+          }
+        p_frag[0] = pack_bf16(p[0][0], p[0][1]);
+        p_frag[1] = pack_bf16(p[0][2], p[0][3]);
+        p_frag[2] = pack_bf16(p[1][0], p[1][1]);
+        p_frag[3] = pack_bf16(p[1][2], p[1][3]);
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float sum = row_sum[r];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l_run[r] = l_run[r] * corr[r] + sum;
+      }
+      if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // the running max rarely moves
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) {
+          o_acc[j][0] *= corr[0]; o_acc[j][1] *= corr[0];
+          o_acc[j][2] *= corr[1]; o_acc[j][3] *= corr[1];
+        }
       }
     }
     // O += P V : V rows are keys (k), columns dims (n): transposed 8x8 loads give the B fragments
@@ -245,7 +271,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     float mx = -INFINITY;
     for (int w = 0; w < NWARPS; ++w) mx = fmaxf(mx, ml_s[(w * ROWS + row) * 2]);
     m_all[r] = mx;
-    f[r] = (m_run[r] == -INFINITY) ? 0.f : expf(m_run[r] - mx);
+    f[r] = sigmoid ? 1.f : (m_run[r] == -INFINITY) ? 0.f : expf(m_run[r] - mx);
   }
   for (int w = 0; w < NWARPS; ++w) {
     if (warp == w) {
@@ -276,7 +302,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       if (mw != -INFINITY) l += ml_s[(w * ROWS + row) * 2 + 1] * expf(mw - mx);
     }
     const float o = o_s[row * HD + d];
-    if (max_splits > 1) {
+    if (sigmoid) {
+      part_acc[((th0 + row) * max_splits + split) * HD + d] = o;
+    } else if (max_splits > 1) {
       part_acc[((th0 + row) * max_splits + split) * HD + d] = o;
       if (d == 0) {
         float* ml = part_ml + ((th0 + row) * max_splits + split) * 2;
@@ -293,8 +321,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 template <int HD>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
                   const int* seq_of_token, const int* positions, void* out, int n_tokens, int nh, int nkv,
-                  int page_size, int chunk, int window, float scale, int sink, int split_size, int max_splits,
-                  float* part_acc, float* part_ml, cudaStream_t stream) {
+                  int page_size, int chunk, int window, float scale, int sink, const float* head_bias, int split_size,
+                  int max_splits, float* part_acc, float* part_ml, cudaStream_t stream) {
   constexpr int STRIDE = HD + 8;
   const size_t smem = (size_t)(ROWS * STRIDE + 4 * TILE * STRIDE) * sizeof(__nv_bfloat16) +
                       (size_t)(NWARPS * ROWS * 2) * sizeof(float);
@@ -304,8 +332,8 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
   dim3 grid(max_splits, nkv, n_tokens);
   attn_decode_kernel<HD><<<grid, NWARPS * 32, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_stride,
-      seq_of_token, positions, (__nv_bfloat16*)out, nh, nkv, page_size, chunk, window, scale, sink, split_size, max_splits,
-      part_acc, part_ml);
+      seq_of_token, positions, (__nv_bfloat16*)out, nh, nkv, page_size, chunk, window, scale, sink, head_bias, split_size,
+      max_splits, part_acc, part_ml);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }
@@ -318,21 +346,21 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
 extern "C" int hb_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                    int table_stride, const int* seq_of_token, const int* positions, void* out,
                                    int n_tokens, int nh, int nkv, int hd, int page_size, int chunk, int window,
-                                   float scale, int sink, int split_size, int max_splits, float* part_acc,
-                                   float* part_ml, cudaStream_t stream) {
+                                   float scale, int sink, const float* head_bias, int split_size, int max_splits,
+                                   float* part_acc, float* part_ml, cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !seq_of_token || !positions || !out) return HB_ERR_BAD_ARG;
   if (n_tokens < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || table_stride <= 0 || chunk < 0 ||
       window < 0 || max_splits < 1 || split_size <= 0 || split_size % TILE != 0)
     return HB_ERR_BAD_ARG;
-  if (max_splits > 1 && (!part_acc || !part_ml)) return HB_ERR_BAD_ARG;
+  if (sink == 2 ? !part_acc : (max_splits > 1 && (!part_acc || !part_ml))) return HB_ERR_BAD_ARG;
   if (nh / nkv > ROWS || n_tokens > 65535 || nkv > 65535) return HB_ERR_UNSUPPORTED;
   if (n_tokens == 0) return HB_OK;
   if (hd == 128)
     return launch_decode<128>(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
-                              nh, nkv, page_size, chunk, window, scale, sink, split_size, max_splits, part_acc, part_ml, stream);
+                              nh, nkv, page_size, chunk, window, scale, sink, head_bias, split_size, max_splits, part_acc, part_ml, stream);
   if (hd == 64)
     return launch_decode<64>(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
-                             nh, nkv, page_size, chunk, window, scale, sink, split_size, max_splits, part_acc, part_ml, stream);
+                             nh, nkv, page_size, chunk, window, scale, sink, head_bias, split_size, max_splits, part_acc, part_ml, stream);
   return HB_ERR_UNSUPPORTED;
 }
 
@@ -406,7 +434,7 @@ extern "C" int hb_attention_decode_static(const void* q, const void* k_pages, co
     if (rc != HB_OK) return rc;
   }
   int rc = hb_attention_decode(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
-                               nh, nkv, hd, page_size, chunk, window, scale, 0, split_size, max_splits, acc, ml, stream);
+                               nh, nkv, hd, page_size, chunk, window, scale, 0, nullptr, split_size, max_splits, acc, ml, stream);
   if (rc != HB_OK || max_splits == 1 || n_tokens == 0) return rc;
   return hb_attention_merge(acc, ml, out, HB_DTYPE_BF16, n_tokens * nh, hd, max_splits, 0, stream);
 }

@@ -53,7 +53,11 @@ struct Args {
   int key_splits;
   float* part_acc;
   float* part_ml;
-  int sink;                  // the denominator has one more term, e^0 (a key of score 0 without a value)
+  int sink;                  // 1: the denominator has one more term, e^0 (a key of score 0 without a value)
+  // sink == 2: sigmoid weights. A key weighs sigmoid(score + head_bias[head]) = 1 / (1 + 2^-(raw * scale_log2 +
+  // bias * log2 e)); nothing is normalised; every block leaves its plain sums in part_acc (zero-filled by the
+  // caller, also with key_splits == 1) and the caller adds the splits.
+  const float* head_bias;
 };
 
 template <int HD>
@@ -101,7 +105,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int n_valid = min(BQ, seq_end - tok0);
   if (n_valid <= 0) return;
   // a row that this block leaves out weighs nothing in the merge
+  const bool sigmoid = a.sink == 2;
   auto no_part = [&](int row) {
+    if (sigmoid) return;                        // part_acc was zero-filled: the row adds nothing
     float* ml = a.part_ml + (((size_t)(tok0 + row) * a.nh + h) * a.key_splits + piece) * 2;
     ml[0] = -INFINITY;
     ml[1] = 0.f;
@@ -236,6 +242,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int pos = p_first + r;
     const int lo = first_visible(pos);
     float m = -INFINITY, l = 0.f;
+    const float bias_log2 = (sigmoid && a.head_bias) ? a.head_bias[h] * 1.4426950408889634f : 0.f;
     bool ok = true;
     for (int j = 0; j < nt && ok; ++j) {
       const int sb = j & 1;
@@ -264,7 +271,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           sv[32 + i] = __uint_as_float(raw1[i]);
         }
       }
-      if (interior) {
+      if (interior && sigmoid) {
+        // nothing to mask and no maximum to follow
+      } else if (interior) {
         float top = -INFINITY;
 #pragma unroll
         for (int i = 0; i < BKEYS; ++i) top = fmaxf(top, sv[i]);
@@ -287,7 +296,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // moves (and O and l are rescaled) only when some row of the warp has grown by more than
       // 2^8, so P stays below 256 and most tiles skip the pass over O. The result is the same
       // sum, scaled by a common factor that the final division removes.
-      const bool move = __any_sync(0xffffffffu, mx > m + 8.f || m == -INFINITY);
+      const bool move = !sigmoid && __any_sync(0xffffffffu, mx > m + 8.f || m == -INFINITY);
       float corr = 1.f;
       if (move) {
         corr = (m == -INFINITY) ? 0.f : fast_exp2(m - mx);
@@ -296,7 +305,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // p = 2^(raw * scale - m): one fused multiply-add and one ex2 per score; a masked score is
       // -inf and gives 0 (m is finite here unless the whole row is still masked)
       float sum = 0.f;
-      if (m == -INFINITY) {
+      if (sigmoid) {
+        // p = 1 / (1 + 2^-(raw * scale_log2 + bias_log2)); a masked score is -inf: 2^inf = inf and p = 0
+#pragma unroll
+        for (int i = 0; i < BKEYS; ++i)
+          sv[i] = __fdividef(1.f, 1.f + fast_exp2(-fmaf(sv[i], a.scale_log2, bias_log2)));
+      } else if (m == -INFINITY) {
 #pragma unroll
         for (int i = 0; i < BKEYS; ++i) sv[i] = 0.f;
       } else {
@@ -382,10 +396,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) atomicExch(a.status, 18);
       } else {
         tc::fence_after();
-        if (a.key_splits > 1) {
+        if (a.key_splits > 1 || sigmoid) {
           // this share of the keys only: the row as it is, with its max and sum, for the merge
           const size_t at = ((size_t)(tok0 + r) * a.nh + h) * a.key_splits + piece;
-          if (row_ok) {
+          if (row_ok && !sigmoid) {
             a.part_ml[at * 2] = m == -INFINITY ? -INFINITY : m * 0.6931471805599453f;
             a.part_ml[at * 2 + 1] = l;
           }
@@ -465,19 +479,19 @@ extern "C" int hb_attention_prefill_tc(const void* q, const void* k_pages, const
                                        int table_stride, const int* cu_seqlens, const int* positions, void* out,
                                        int n_tokens, int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd,
                                        int page_size, int chunk, int window, float scale, int skip_single,
-                                       int sink, int key_splits, float* part_acc, float* part_ml, int* status,
-                                       cudaStream_t stream) {
+                                       int sink, const float* head_bias, int key_splits, float* part_acc,
+                                       float* part_ml, int* status, cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !cu_seqlens || !positions || !out || !status) return HB_ERR_BAD_ARG;
   if (n_tokens < 0 || n_pages <= 0 || n_seqs < 0 || max_new < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 ||
       page_size <= 0 || table_stride <= 0 || chunk < 0 || window < 0 || key_splits < 1 || key_splits > 64 ||
-      (key_splits > 1 && (!part_acc || !part_ml)))
+      (sink == 2 ? !part_acc : (key_splits > 1 && (!part_acc || !part_ml))))
     return HB_ERR_BAD_ARG;
   if (page_size % 16 != 0 || !(BKEYS % page_size == 0 || page_size % BKEYS == 0)) return HB_ERR_UNSUPPORTED;
   if (n_seqs > 65535 || nh > 65535) return HB_ERR_UNSUPPORTED;
   if (!(scale > 0.f)) return HB_ERR_UNSUPPORTED;       // the largest raw score is taken for the largest scaled one
   if (n_seqs == 0 || max_new == 0 || n_tokens == 0) return HB_OK;
   Args a{block_table, cu_seqlens, positions, (__nv_bfloat16*)out, status, table_stride, nh, nkv, page_size, chunk,
-         window, skip_single, page_size < BKEYS ? page_size : BKEYS, scale * 1.4426950408889634f, key_splits, part_acc, part_ml, sink};
+         window, skip_single, page_size < BKEYS ? page_size : BKEYS, scale * 1.4426950408889634f, key_splits, part_acc, part_ml, sink, head_bias};
   const long long pool_rows = (long long)n_pages * nkv * page_size;
   if (hd == 128) return launch<128>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
   if (hd == 64) return launch<64>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);

@@ -188,3 +188,25 @@ extern "C" int hb_sigmoid_attention(const void* q, int dtype, const void* k_page
   }
   return HB_OK;
 }
+
+extern "C" int hb_sigmoid_merge(const float* part_acc, const int* positions, const float* v_inv_freq, int v_pairs,
+                                int v_interleaved, void* out, int dtype, int n_tokens, int nh, int hd, int max_splits,
+                                cudaStream_t stream) {
+  if (!part_acc || !positions || !out || n_tokens < 0 || nh <= 0 || hd <= 0 || max_splits < 1 || v_pairs < 0 ||
+      2 * v_pairs > hd)
+    return HB_ERR_BAD_ARG;
+  if (!v_inv_freq) v_pairs = 0;
+  if (n_tokens == 0) return HB_OK;
+  if ((long long)n_tokens * nh > 0x7fffffffLL) return HB_ERR_UNSUPPORTED;
+  const size_t msmem = (size_t)hd * sizeof(float);
+  if (dtype == HB_DTYPE_F32)
+    sigmoid_merge_kernel<float><<<n_tokens * nh, 128, msmem, stream>>>(part_acc, positions, v_inv_freq, v_pairs,
+                                                                       v_interleaved, (float*)out, nh, hd, max_splits);
+  else if (dtype == HB_DTYPE_BF16)
+    sigmoid_merge_kernel<__nv_bfloat16><<<n_tokens * nh, 128, msmem, stream>>>(
+        part_acc, positions, v_inv_freq, v_pairs, v_interleaved, (__nv_bfloat16*)out, nh, hd, max_splits);
+  else
+    return HB_ERR_BAD_ARG;
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}

@@ -28,11 +28,12 @@ _SIGNATURES = {
     "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, I, I, F, P, I, I, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
     "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P],
     "hb_attention_merge": [P, P, P, I, I, I, I, I, P],
-    "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P],
+    "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, I, I, P, P, P],
     "hb_attention_decode_tma": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
     "hb_attention_decode_fused": [P, P, I, I, I, F, I, F, F, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P, P, I, F, I, P],
     "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
-    "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
+    "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P, I, P, P, P, P],
+    "hb_sigmoid_merge": [P, P, P, I, I, P, I, I, I, I, I, P],
     "hb_router_topk": [P, I, P, I, I, I, I, I, I, F, P, P, P, P],
     "hb_moe_plan": [P, I, I, P, P, P, P, P],
     "hb_router_plan": [P, I, P, I, I, I, I, I, I, F, P, P, P, P, P, P, P, P, P],
@@ -854,6 +855,88 @@ def sigmoid_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     return out
 
 
+def sigmoid_merge(part_acc: torch.Tensor, positions: torch.Tensor, out_dtype: torch.dtype,
+                  v_inv_freq: Optional[torch.Tensor] = None, v_interleaved: bool = False) -> torch.Tensor:
+    """part_acc float32 [N, nh, splits, hd] -> [N, nh, hd]: the splits of every (token, head) added in split order,
+    then (``v_inv_freq``) the sum turned back by the token's position."""
+    _need(part_acc, "part_acc", torch.float32); _need(positions, "positions", torch.int32)
+    n, nh, splits, hd = part_acc.shape
+    v_pairs = 0
+    if v_inv_freq is not None:
+        _need(v_inv_freq, "v_inv_freq", torch.float32)
+        v_pairs = v_inv_freq.numel()
+    out = torch.empty((n, nh, hd), dtype=out_dtype, device=part_acc.device)
+    _check(lib().hb_sigmoid_merge(_ptr(part_acc), _ptr(positions), _ptr(v_inv_freq), v_pairs, int(v_interleaved), _ptr(out),
+                                  _dt(out), n, nh, hd, splits, _stream()), "sigmoid_merge")
+    return out
+
+
+def sigmoid_attention_tc_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int, page_size: int) -> bool:
+    """Shapes the tensor-core kernels take with sigmoid weights: those of the decode kernel and of the tcgen05
+    prefill kernel at once."""
+    return decode_attention_supported(q_dtype, nh, nkv, hd) and prefill_attention_tc_supported(q_dtype, nh, nkv, hd, page_size)
+
+
+def sigmoid_decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                             seq_of_token: torch.Tensor, positions: torch.Tensor, chunk: int, window: int, scale: float,
+                             head_bias: torch.Tensor, max_context: int, v_inv_freq: Optional[torch.Tensor] = None,
+                             v_interleaved: bool = False) -> torch.Tensor:
+    """:func:`sigmoid_attention` for a batch of single decoded tokens in bfloat16 on the tensor cores: the decode
+    kernel of :func:`decode_attention` with sigmoid weights (the query heads of a kv head in one tile, the keys cut
+    into splits as there); the splits' plain sums are added and turned back by :func:`sigmoid_merge`."""
+    _need(q, "q", torch.bfloat16); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
+    _need(head_bias, "head_bias", torch.float32)
+    for t, nm in ((block_table, "block_table"), (seq_of_token, "seq_of_token"), (positions, "positions")):
+        _need(t, nm, torch.int32)
+    n, nh, hd = q.shape
+    _, nkv, page_size, hd2 = k_pages.shape
+    if hd2 != hd or k_pages.shape != v_pages.shape or head_bias.numel() != nh:
+        raise KernelError("cache pages or head_bias do not match the query's heads")
+    if not decode_attention_supported(q.dtype, nh, nkv, hd):
+        raise KernelError(f"decode attention does not take nh={nh} nkv={nkv} head_dim={hd}")
+    longest = max(int(max_context), 1)
+    if chunk > 0:
+        longest = min(longest, chunk)
+    if window > 0:
+        longest = min(longest, window)
+    split_size, splits = _decode_splits(longest, n * nkv)
+    part_acc = torch.empty((n, nh, splits, hd), dtype=torch.float32, device=q.device)
+    _check(lib().hb_attention_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                                     _ptr(seq_of_token), _ptr(positions), _ptr(part_acc), n, nh, nkv, hd, page_size,
+                                     int(chunk), int(window), float(scale), 2, _ptr(head_bias), split_size, splits,
+                                     _ptr(part_acc), None, _stream()), "attention_decode")
+    return sigmoid_merge(part_acc, positions, q.dtype, v_inv_freq, v_interleaved)
+
+
+def sigmoid_prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                                 cu_seqlens: torch.Tensor, positions: torch.Tensor, n_seqs: int, max_new: int, chunk: int,
+                                 window: int, scale: float, head_bias: torch.Tensor, skip_single: bool = False,
+                                 v_inv_freq: Optional[torch.Tensor] = None, v_interleaved: bool = False) -> torch.Tensor:
+    """:func:`sigmoid_attention` for portions of prompts in bfloat16 on tcgen05: the kernel of
+    :func:`prefill_attention_tc` with sigmoid weights; its rows leave as float32 sums and :func:`sigmoid_merge` turns
+    them back. Rows of requests that bring one token are zero with ``skip_single``."""
+    _need(q, "q", torch.bfloat16); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
+    _need(head_bias, "head_bias", torch.float32)
+    for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (positions, "positions")):
+        _need(t, nm, torch.int32)
+    n, nh, hd = q.shape
+    n_pages, nkv, page_size, hd2 = k_pages.shape
+    if hd2 != hd or k_pages.shape != v_pages.shape or head_bias.numel() != nh:
+        raise KernelError("cache pages or head_bias do not match the query's heads")
+    if not prefill_attention_tc_supported(q.dtype, nh, nkv, hd, page_size):
+        raise KernelError(f"tcgen05 prefill attention does not take nh={nh} nkv={nkv} head_dim={hd} page={page_size}")
+    if cu_seqlens.numel() != n_seqs + 1 or block_table.shape[0] < n_seqs:
+        raise KernelError("cu_seqlens / block_table do not match the number of requests")
+    part_acc = torch.zeros((n, nh, 1, hd), dtype=torch.float32, device=q.device)
+    _check(lib().hb_attention_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                                         block_table.shape[1], _ptr(cu_seqlens), _ptr(positions), _ptr(part_acc), n, n_pages,
+                                         n_seqs, int(max_new), nh, nkv, hd, page_size, int(chunk), int(window),
+                                         float(scale), int(skip_single), 2, _ptr(head_bias), 1, _ptr(part_acc), None,
+                                         _ptr(_tc_status(q.device)), _stream()), "attention_prefill_tc")
+    TC_USED[0] = True
+    return sigmoid_merge(part_acc, positions, q.dtype, v_inv_freq, v_interleaved)
+
+
 def _decode_splits(longest: int, groups: int) -> Tuple[int, int]:
     """How to cut ``longest`` keys for ``groups`` (token, kv head) pairs: the number of splits
     that minimises waves x (tiles per block + a block's fixed cost) + a cost per split (the
@@ -911,7 +994,7 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     if code == _UNSUPPORTED:
         code = lib().hb_attention_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                                          _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv, hd, page_size,
-                                         int(chunk), int(window), float(scale), int(sink), split_size, splits,
+                                         int(chunk), int(window), float(scale), int(sink), None, split_size, splits,
                                          _ptr(part_acc), _ptr(part_ml), _stream())
         _check(code, "attention_decode")
     else:
@@ -1072,7 +1155,7 @@ def prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
     _check(lib().hb_attention_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                                          block_table.shape[1], _ptr(cu_seqlens), _ptr(positions), _ptr(out), n, n_pages,
                                          n_seqs, int(max_new), nh, nkv, hd, page_size, int(chunk), int(window),
-                                         float(scale), int(skip_single), int(sink), key_splits,
+                                         float(scale), int(skip_single), int(sink), None, key_splits,
                                          _ptr(part_acc) if part_acc is not None else None,
                                          _ptr(part_ml) if part_ml is not None else None, _ptr(_tc_status(q.device)),
                                          _stream()),

@@ -81,6 +81,35 @@ def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, 
                                chunk, sliding, scale, ctx.max_context, sink=sink)
 
 
+def sigmoid_attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, hd: int, chunk: int,
+                              sliding: int, scale: float, head_bias, v_inv_freq, v_interleaved: bool):
+    """sum_j sigmoid(q . k_j scale + head_bias) v_j over the keys each token may read, turned back by the token's
+    position where the values are cached rotated, by the kernel that fits the step, as :func:`attend_over_pages`
+    chooses for the softmax: the tensor-core decode kernel for single tokens, the tcgen05 kernel for portions of
+    at least a tile of new tokens (single tokens beside them through the decode kernel), the general kernel for the
+    rest (float32, other head sizes, short portions)."""
+    positions = ctx.positions
+    if ops.sigmoid_attention_tc_supported(q.dtype, nh, nkv, hd, ctx.page_size):
+        if ctx.max_new == 1:
+            return ops.sigmoid_decode_attention(q, k_pages, v_pages, block_table, ctx.seq_of_token, positions, chunk,
+                                                sliding, scale, head_bias, ctx.max_context, v_inv_freq, v_interleaved)
+        if ctx.max_new >= ops.PREFILL_TC_MIN_TOKENS:
+            single = ctx.decode_rows is not None
+            o = ops.sigmoid_prefill_attention_tc(q, k_pages, v_pages, block_table, ctx.cu_seqlens, positions, ctx.n_seqs,
+                                                 ctx.max_new, chunk, sliding, scale, head_bias, skip_single=single,
+                                                 v_inv_freq=v_inv_freq, v_interleaved=v_interleaved)
+            if single:
+                rows = ctx.decode_rows
+                od = ops.sigmoid_decode_attention(q.index_select(0, rows), k_pages, v_pages, block_table,
+                                                  ctx.seq_of_token.index_select(0, rows), positions.index_select(0, rows),
+                                                  chunk, sliding, scale, head_bias, ctx.decode_max_context, v_inv_freq,
+                                                  v_interleaved)
+                o.index_copy_(0, rows, od)
+            return o
+    return ops.sigmoid_attention(q, k_pages, v_pages, block_table, ctx.seq_of_token, positions, chunk, sliding, scale,
+                                 head_bias, ctx.max_context, v_inv_freq=v_inv_freq, v_interleaved=v_interleaved)
+
+
 @register("mixer", "attention")
 class AttentionMixer(Part):
     """q/k/v projections, position encoding or temperature, optional weightless q/k norm, cache
@@ -238,9 +267,8 @@ class AttentionMixer(Part):
                              k_norm_weight=self.w_knorm, norm_first=self.norm_weighted,
                              norm_dim=0 if plain else self.dim, rot_mul=rot_mul, v_inv_freq=self._v_table,
                              v_interleaved=v_inter)
-            o = ops.sigmoid_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions, chunk,
-                                      sliding, self.scale, self.head_bias, ctx.max_context, v_inv_freq=self._v_table,
-                                      v_interleaved=v_inter)
+            o = sigmoid_attend_over_pages(q, cache.k_pages, cache.v_pages, block_table, ctx, self.nh, self.nkv, self.hd,
+                                          chunk, sliding, self.scale, self.head_bias, self._v_table, v_inter)
             return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o, bias=self.b_o)
         if self.hd == self.dim and ctx.max_new == 1 and cache.writes and self.FUSED_DECODE and qkv.dtype == torch.bfloat16:
             # a step of single decoded tokens: encoding, cache append, attention and the merge of its

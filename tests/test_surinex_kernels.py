@@ -207,6 +207,55 @@ def test_sigmoid_attention_over_pages(dt, tol, nh, nkv, hd, vdim):
             close(got, want, tol, f"start {start}, {n} tokens, split {splits}")
 
 
+@pytest.mark.parametrize("page", [16, 64])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (8, 2, 128), (16, 1, 128)])
+def test_sigmoid_attention_on_the_tensor_cores(nh, nkv, hd, page):
+    """bfloat16 heads of 64 and 128: single tokens of three requests at different depths through the decode kernel
+    (keys cut into splits), and portions of 130 to 300 new tokens at the start and far into a context through the
+    tcgen05 kernel, one request bringing a single token beside them; all against the plain sum."""
+    from hi_b200.kernels import ops
+
+    dt, scale = torch.bfloat16, hd ** -0.5
+    g = torch.Generator().manual_seed(nh + hd + page)
+    lens = (900, 300, 65)
+    per = -(-max(lens) // page)
+    perm = torch.randperm(3 * per + 4, generator=g)[: 3 * per].view(3, per)
+    kp = torch.zeros((3 * per + 4, nkv, page, hd), dtype=dt, device=DEV)
+    vp = torch.zeros_like(kp)
+    ks, vs = [], []
+    for r, n in enumerate(lens):
+        k, v = torch.randn(n, nkv, hd, generator=g).to(dt), torch.randn(n, nkv, hd, generator=g).to(dt)
+        ks.append(k.float()); vs.append(v.float())
+        for p in range(n):
+            kp[perm[r, p // page], :, p % page] = k[p].to(DEV)
+            vp[perm[r, p // page], :, p % page] = v[p].to(DEV)
+    table = perm.to(torch.int32).to(DEV)
+    bias = (torch.randn(nh, generator=g) - 4.0)
+    vf = torch.tensor([1000.0 ** (-2.0 * m / hd) for m in range(hd // 2)])
+    # single tokens: the last position of every request
+    q = torch.randn(3, nh, hd, generator=g).to(dt)
+    got = ops.sigmoid_decode_attention(q.to(DEV), kp, vp, table, i32([0, 1, 2]), i32([n - 1 for n in lens]), 0, 0, scale,
+                                       bias.to(DEV), max(lens), vf.to(DEV), True)
+    for r, n in enumerate(lens):
+        want = plain_sigmoid_attention(q[r: r + 1].float(), ks[r], vs[r], bias, scale, nh // nkv, vf, True, n - 1)
+        close(got[r: r + 1], want, 2e-2, f"single token of request {r}")
+    # portions: request 0 brings positions 600..899, request 1 its first 130, request 2 one token
+    news = ((600, 300), (0, 130), (64, 1))
+    qs = [torch.randn(n, nh, hd, generator=g).to(dt) for _s, n in news]
+    cu = [0, 300, 430, 431]
+    pos = [p for s0, n in news for p in range(s0, s0 + n)]
+    for skip in (False, True):
+        got = ops.sigmoid_prefill_attention_tc(torch.cat(qs).to(DEV), kp, vp, table, i32(cu), i32(pos), 3, 300, 0, 0, scale,
+                                               bias.to(DEV), skip_single=skip, v_inv_freq=vf.to(DEV), v_interleaved=True)
+        for r, (s0, n) in enumerate(news):
+            want = plain_sigmoid_attention(qs[r].float(), ks[r], vs[r], bias, scale, nh // nkv, vf, True, s0)
+            if skip and n == 1:
+                assert float(got[cu[r]: cu[r + 1]].abs().max()) == 0.0
+            else:
+                close(got[cu[r]: cu[r + 1]], want, 2e-2, f"portion of request {r}, skip {skip}")
+    ops.check_tc_status()
+
+
 # --------------------------------------------------------------------------- recurrences
 @pytest.mark.parametrize("heads,dim,vdim,general", [(2, 16, 24, False), (3, 5, 7, False), (1, 136, 20, False), (2, 48, 32, True)])
 def test_gated_linear_attention_inputs_and_recurrence(heads, dim, vdim, general):
