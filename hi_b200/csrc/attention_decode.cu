@@ -98,40 +98,38 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const bool ok = r < G;
     cp_async16(q_s + r * STRIDE + ch * 8, q + (th0 + (ok ? r : 0)) * HD + ch * 8, ok);
   }
-  // thread -> one 16-byte chunk column and every (128 / CHUNKS)-th row of a tile. When a tile
-  // never straddles a page (page_size a multiple of TILE and the range starts on a TILE
-  // boundary) one table lookup serves the whole tile.
-  constexpr int ROWS_PER_PASS = NWARPS * 32 / CHUNKS;
-  const int ld_ch = tid % CHUNKS, ld_r0 = tid / CHUNKS;
+  // thread -> every 128th 16-byte chunk of a [TILE][CHUNKS] tile. When a tile never straddles a page (page_size
+  // a multiple of TILE and the range starts on a TILE boundary) one table lookup serves the whole tile.
+  static_assert((TILE * CHUNKS) % (NWARPS * 32) == 0, "whole passes of the block");
   const bool tile_in_page = (page_size % TILE == 0) && (first % TILE == 0);
   auto load_tile = [&](int tile, int buf) {
     const int base = first + tile * TILE;
-    __nv_bfloat16* kd = k_s + (buf * TILE + ld_r0) * STRIDE + ld_ch * 8;
-    __nv_bfloat16* vd = v_s + (buf * TILE + ld_r0) * STRIDE + ld_ch * 8;
+    __nv_bfloat16* kd = k_s + buf * TILE * STRIDE;
+    __nv_bfloat16* vd = v_s + buf * TILE * STRIDE;
     if (tile_in_page) {
       const int page = table[base / page_size];
-      const size_t off0 = (((size_t)(page >= 0 ? page : 0) * nkv + kvh) * page_size + (base % page_size) + ld_r0) * HD + ld_ch * 8;
-      const __nv_bfloat16* ks = k_pages + off0;
-      const __nv_bfloat16* vs = v_pages + off0;
+      const size_t off0 = (((size_t)(page >= 0 ? page : 0) * nkv + kvh) * page_size + (base % page_size)) * HD;
 #pragma unroll
-      for (int i = 0; i < TILE / ROWS_PER_PASS; ++i) {
-        const bool ok = page >= 0 && base + ld_r0 + i * ROWS_PER_PASS <= last;
-        cp_async16(kd + i * ROWS_PER_PASS * STRIDE, ks + (size_t)i * ROWS_PER_PASS * HD, ok);
-        cp_async16(vd + i * ROWS_PER_PASS * STRIDE, vs + (size_t)i * ROWS_PER_PASS * HD, ok);
+      for (int i = 0; i < TILE * CHUNKS / (NWARPS * 32); ++i) {
+        const int c = tid + i * NWARPS * 32, r = c / CHUNKS, ch = c % CHUNKS;
+        const bool ok = page >= 0 && base + r <= last;
+        cp_async16(kd + r * STRIDE + ch * 8, k_pages + off0 + (size_t)r * HD + ch * 8, ok);
+        cp_async16(vd + r * STRIDE + ch * 8, v_pages + off0 + (size_t)r * HD + ch * 8, ok);
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < TILE / ROWS_PER_PASS; ++i) {
-        const int key = base + ld_r0 + i * ROWS_PER_PASS;
+      for (int i = 0; i < TILE * CHUNKS / (NWARPS * 32); ++i) {
+        const int c = tid + i * NWARPS * 32, r = c / CHUNKS, ch = c % CHUNKS;
+        const int key = base + r;
         bool ok = key <= last;
         size_t off = 0;
         if (ok) {
           const int page = table[key / page_size];
           ok = page >= 0;
-          off = (((size_t)(ok ? page : 0) * nkv + kvh) * page_size + (key % page_size)) * HD + ld_ch * 8;
+          off = (((size_t)(ok ? page : 0) * nkv + kvh) * page_size + (key % page_size)) * HD + ch * 8;
         }
-        cp_async16(kd + i * ROWS_PER_PASS * STRIDE, k_pages + off, ok);
-        cp_async16(vd + i * ROWS_PER_PASS * STRIDE, v_pages + off, ok);
+        cp_async16(kd + r * STRIDE + ch * 8, k_pages + off, ok);
+        cp_async16(vd + r * STRIDE + ch * 8, v_pages + off, ok);
       }
     }
   };
@@ -340,7 +338,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
 
 }  // namespace
 
-// bfloat16 only; head_dim 64 or 128; at most 16 query heads per kv head; every token is taken
+// bfloat16 only; head_dim 64, 128 or 192; at most 16 query heads per kv head; every token is taken
 // as one decode row. Returns HB_ERR_UNSUPPORTED for other shapes (the caller then uses the
 // general kernel). The merge over splits is hb_attention_merge.
 extern "C" int hb_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
@@ -355,6 +353,9 @@ extern "C" int hb_attention_decode(const void* q, const void* k_pages, const voi
   if (sink == 2 ? !part_acc : (max_splits > 1 && (!part_acc || !part_ml))) return HB_ERR_BAD_ARG;
   if (nh / nkv > ROWS || n_tokens > 65535 || nkv > 65535) return HB_ERR_UNSUPPORTED;
   if (n_tokens == 0) return HB_OK;
+  if (hd == 192)
+    return launch_decode<192>(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
+                              nh, nkv, page_size, chunk, window, scale, sink, head_bias, split_size, max_splits, part_acc, part_ml, stream);
   if (hd == 128)
     return launch_decode<128>(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
                               nh, nkv, page_size, chunk, window, scale, sink, head_bias, split_size, max_splits, part_acc, part_ml, stream);

@@ -26,7 +26,6 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     float scale, int skip_single, int sink) {
   constexpr int STRIDE = HD + 8;
   constexpr int CHUNKS = HD / 8;
-  constexpr int ROWS_PER_PASS = NWARPS * 32 / CHUNKS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [BQ][STRIDE]
   __nv_bfloat16* k_s = q_s + BQ * STRIDE;                            // [2][TILE][STRIDE]
@@ -53,38 +52,42 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int tile_end = p_last / TILE;                      // inclusive
   const bool tile_in_page = (page_size % TILE) == 0;
 
-  const int ld_ch = tid % CHUNKS, ld_r0 = tid / CHUNKS;
-  for (int r = ld_r0; r < BQ; r += ROWS_PER_PASS) {
+  // the query rows, then tiles of keys and values: thread -> every 128th 16-byte chunk of the [rows][CHUNKS] tile
+  static_assert((BQ * CHUNKS) % (NWARPS * 32) == 0 && (TILE * CHUNKS) % (NWARPS * 32) == 0, "whole passes of the block");
+#pragma unroll
+  for (int i = 0; i < BQ * CHUNKS / (NWARPS * 32); ++i) {
+    const int c = tid + i * NWARPS * 32, r = c / CHUNKS, ch = c % CHUNKS;
     const bool ok = r < n_valid;
-    hb::cp_async16(q_s + r * STRIDE + ld_ch * 8, q + ((size_t)(tok0 + (ok ? r : 0)) * nh + h) * HD + ld_ch * 8, ok);
+    hb::cp_async16(q_s + r * STRIDE + ch * 8, q + ((size_t)(tok0 + (ok ? r : 0)) * nh + h) * HD + ch * 8, ok);
   }
   auto load_tile = [&](int kt, int buf) {
     const int base = kt * TILE;
-    __nv_bfloat16* kd = k_s + (buf * TILE + ld_r0) * STRIDE + ld_ch * 8;
-    __nv_bfloat16* vd = v_s + (buf * TILE + ld_r0) * STRIDE + ld_ch * 8;
+    __nv_bfloat16* kd = k_s + buf * TILE * STRIDE;
+    __nv_bfloat16* vd = v_s + buf * TILE * STRIDE;
     if (tile_in_page) {
       const int page = table[base / page_size];
-      const size_t off0 =
-          (((size_t)(page >= 0 ? page : 0) * nkv + kvh) * page_size + (base % page_size) + ld_r0) * HD + ld_ch * 8;
+      const size_t off0 = (((size_t)(page >= 0 ? page : 0) * nkv + kvh) * page_size + (base % page_size)) * HD;
 #pragma unroll
-      for (int i = 0; i < TILE / ROWS_PER_PASS; ++i) {
-        const bool ok = page >= 0 && base + ld_r0 + i * ROWS_PER_PASS <= p_last;
-        hb::cp_async16(kd + i * ROWS_PER_PASS * STRIDE, k_pages + off0 + (size_t)i * ROWS_PER_PASS * HD, ok);
-        hb::cp_async16(vd + i * ROWS_PER_PASS * STRIDE, v_pages + off0 + (size_t)i * ROWS_PER_PASS * HD, ok);
+      for (int i = 0; i < TILE * CHUNKS / (NWARPS * 32); ++i) {
+        const int c = tid + i * NWARPS * 32, r = c / CHUNKS, ch = c % CHUNKS;
+        const bool ok = page >= 0 && base + r <= p_last;
+        hb::cp_async16(kd + r * STRIDE + ch * 8, k_pages + off0 + (size_t)r * HD + ch * 8, ok);
+        hb::cp_async16(vd + r * STRIDE + ch * 8, v_pages + off0 + (size_t)r * HD + ch * 8, ok);
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < TILE / ROWS_PER_PASS; ++i) {
-        const int key = base + ld_r0 + i * ROWS_PER_PASS;
+      for (int i = 0; i < TILE * CHUNKS / (NWARPS * 32); ++i) {
+        const int c = tid + i * NWARPS * 32, r = c / CHUNKS, ch = c % CHUNKS;
+        const int key = base + r;
         bool ok = key <= p_last;
         size_t off = 0;
         if (ok) {
           const int page = table[key / page_size];
           ok = page >= 0;
-          off = (((size_t)(ok ? page : 0) * nkv + kvh) * page_size + (key % page_size)) * HD + ld_ch * 8;
+          off = (((size_t)(ok ? page : 0) * nkv + kvh) * page_size + (key % page_size)) * HD + ch * 8;
         }
-        hb::cp_async16(kd + i * ROWS_PER_PASS * STRIDE, k_pages + off, ok);
-        hb::cp_async16(vd + i * ROWS_PER_PASS * STRIDE, v_pages + off, ok);
+        hb::cp_async16(kd + r * STRIDE + ch * 8, k_pages + off, ok);
+        hb::cp_async16(vd + r * STRIDE + ch * 8, v_pages + off, ok);
       }
     }
   };
@@ -241,7 +244,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
 
 }  // namespace
 
-// bfloat16, head_dim 64 or 128. `cu_seqlens` [n_seqs + 1] are the first flat rows of the requests'
+// bfloat16, head_dim 64, 128 or 192. `cu_seqlens` [n_seqs + 1] are the first flat rows of the requests'
 // new tokens, whose positions are consecutive; `max_new` is the longest run. Other shapes:
 // HB_ERR_UNSUPPORTED (the caller uses the general kernel).
 extern "C" int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
@@ -254,6 +257,9 @@ extern "C" int hb_attention_prefill(const void* q, const void* k_pages, const vo
     return HB_ERR_BAD_ARG;
   if (n_seqs > 65535 || nh > 65535) return HB_ERR_UNSUPPORTED;
   if (n_seqs == 0 || max_new == 0) return HB_OK;
+  if (hd == 192)
+    return launch_prefill<192>(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_seqs,
+                               max_new, nh, nkv, page_size, chunk, window, scale, skip_single, sink, stream);
   if (hd == 128)
     return launch_prefill<128>(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_seqs,
                                max_new, nh, nkv, page_size, chunk, window, scale, skip_single, sink, stream);

@@ -69,7 +69,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   constexpr int QBLOCK = BQ * 128;              // bytes of one [128 rows x 64 elements] swizzled block of Q
   constexpr int KVBLOCK = BKEYS * 128;          // the same for a K or V tile (rows = key positions)
   constexpr int S_COLS = BKEYS;                 // columns of one S buffer
-  constexpr int TMEM_COLS = 256;                // S0, S1 (64 columns each), O (HD columns)
+  // S0, S1 (64 columns each), O (HD columns); an allocation is a power of two. Rows over 128 take the whole
+  // tensor memory of the SM, where their shared memory lets one block live anyway.
+  constexpr int TMEM_COLS = 2 * S_COLS + HD <= 256 ? 256 : 512;
+  static_assert(HD % 64 == 0 && 2 * S_COLS + HD <= 512, "rows of 64-element blocks, S and O within tensor memory");
   // No slack for aligning by hand: two blocks per SM only fit without it. The swizzled tiles need
   // a 1024-byte aligned base, which dynamic shared memory has when the kernel has no static
   // shared memory; if it ever has not, the block reports it and leaves.
@@ -469,7 +472,7 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const Args& 
 
 }  // namespace
 
-// bfloat16, head_dim 64 or 128, page_size a multiple of 16 that divides 64 or is a multiple of it.
+// bfloat16, head_dim 64, 128 or 192, page_size a multiple of 16 that divides 64 or is a multiple of it.
 // Arguments as hb_attention_prefill, plus the number of rows of `q`, the number of pages of the
 // pools, `key_splits` (1, or how many blocks share the key tiles of a query tile and head: the rows
 // then go unnormalised to `part_acc` [n_tokens * nh][key_splits][hd] and `part_ml`
@@ -493,6 +496,7 @@ extern "C" int hb_attention_prefill_tc(const void* q, const void* k_pages, const
   Args a{block_table, cu_seqlens, positions, (__nv_bfloat16*)out, status, table_stride, nh, nkv, page_size, chunk,
          window, skip_single, page_size < BKEYS ? page_size : BKEYS, scale * 1.4426950408889634f, key_splits, part_acc, part_ml, sink, head_bias};
   const long long pool_rows = (long long)n_pages * nkv * page_size;
+  if (hd == 192) return launch<192>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
   if (hd == 128) return launch<128>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
   if (hd == 64) return launch<64>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
   return HB_ERR_UNSUPPORTED;

@@ -10,6 +10,8 @@
 //   rmsnorm_mean2  out = (a / rms(a) * w_a + b / rms(b) * w_b) / 2: two mixers side by side
 //
 // Sums and statistics are float32; h stays float32 between the norm and the convolution.
+#include <stdint.h>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -58,6 +60,54 @@ __global__ void canon_conv_kernel(const float* __restrict__ h, const float* __re
     st_any(out_a, dtype, (size_t)t * width + c, own + a);
     if (taps_b) st_any(out_b, dtype, (size_t)t * width + c, own + b);
   }
+}
+
+// The same with four channels a thread (width a multiple of 4): rows of h and the taps of four neighbouring
+// channels ([4][K] floats, contiguous) come as 16-byte loads, results leave as 8- or 16-byte stores.
+template <int K>
+__global__ void canon_conv_vec_kernel(const float* __restrict__ h, const float* __restrict__ taps_a,
+                                      const float* __restrict__ taps_b, const float* __restrict__ state,
+                                      long long state_stride, const int* __restrict__ cu_seqlens,
+                                      const int* __restrict__ seq_of_token, const int* __restrict__ slots,
+                                      void* __restrict__ out_a, void* __restrict__ out_b, int dtype, int width) {
+  const int t = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (c >= width) return;
+  const int s = seq_of_token[t];
+  const int start = cu_seqlens[s];
+  const int local = t - start;
+  const float* tail = state + (size_t)slots[s] * state_stride;      // [K-1, W]
+  float4 x[K];
+#pragma unroll
+  for (int j = 0; j < K; ++j) {
+    const int rel = local - (K - 1) + j;
+    x[j] = *reinterpret_cast<const float4*>(rel >= 0 ? h + (size_t)(start + rel) * width + c
+                                                     : tail + (size_t)(K - 1 + rel) * width + c);
+  }
+  auto run = [&](const float* taps, void* out) {
+    float w[4 * K];
+#pragma unroll
+    for (int i = 0; i < K; ++i) *reinterpret_cast<float4*>(w + 4 * i) = *reinterpret_cast<const float4*>(taps + (size_t)c * K + 4 * i);
+    float4 y = x[K - 1];
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      a0 = fmaf(w[j], x[j].x, a0);
+      a1 = fmaf(w[K + j], x[j].y, a1);
+      a2 = fmaf(w[2 * K + j], x[j].z, a2);
+      a3 = fmaf(w[3 * K + j], x[j].w, a3);
+    }
+    y.x += a0; y.y += a1; y.z += a2; y.w += a3;
+    if (dtype == HB_DTYPE_F32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)t * width + c) = y;
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+      uint2 pack = make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)t * width + c) = pack;
+    }
+  };
+  run(taps_a, out_a);
+  if (taps_b) run(taps_b, out_b);
 }
 
 // The last K-1 rows of h of every request after this step's rows replace its state's.
@@ -111,6 +161,59 @@ __global__ void rmsnorm_mean2_kernel(const void* __restrict__ a, const void* __r
   }
 }
 
+// four neighbouring elements as floats / from floats (16-byte loads of float32, 8-byte ones of bfloat16)
+__device__ __forceinline__ float4 ld4_any(const void* p, int dtype, size_t i) {
+  if (dtype == HB_DTYPE_F32) return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+  const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void st4_any(void* p, int dtype, size_t i, float4 v) {
+  if (dtype == HB_DTYPE_F32) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + i) = v;
+  } else {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p) + i) =
+        make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+  }
+}
+
+// The same, four channels a thread, a row's numbers kept in registers between the two passes (width a multiple of
+// 4, at most 4 * kGroups * blockDim.x; pointers on 16-byte boundaries).
+template <int kGroups>
+__global__ void rmsnorm_mean2_vec_kernel(const void* __restrict__ a, const void* __restrict__ b, int in_dtype,
+                                         const void* __restrict__ wa, const void* __restrict__ wb, int w_dtype, float eps,
+                                         void* __restrict__ out, int out_dtype, int width) {
+  __shared__ float scratch[33];
+  const size_t base = (size_t)blockIdx.x * width;
+  float4 va[kGroups], vb[kGroups];
+  float sa = 0.f, sb = 0.f;
+#pragma unroll
+  for (int g = 0; g < kGroups; ++g) {
+    const int c = (g * blockDim.x + threadIdx.x) * 4;
+    va[g] = vb[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < width) {
+      va[g] = ld4_any(a, in_dtype, base + c);
+      vb[g] = ld4_any(b, in_dtype, base + c);
+    }
+    sa += va[g].x * va[g].x + va[g].y * va[g].y + va[g].z * va[g].z + va[g].w * va[g].w;
+    sb += vb[g].x * vb[g].x + vb[g].y * vb[g].y + vb[g].z * vb[g].z + vb[g].w * vb[g].w;
+  }
+  const float ia = 0.5f * rsqrtf(hb::block_sum(sa, scratch) / (float)width + eps);
+  const float ib = 0.5f * rsqrtf(hb::block_sum(sb, scratch) / (float)width + eps);
+#pragma unroll
+  for (int g = 0; g < kGroups; ++g) {
+    const int c = (g * blockDim.x + threadIdx.x) * 4;
+    if (c < width) {
+      const float4 ga = ld4_any(wa, w_dtype, c), gb = ld4_any(wb, w_dtype, c);
+      st4_any(out, out_dtype, base + c,
+              make_float4(va[g].x * ia * ga.x + vb[g].x * ib * gb.x, va[g].y * ia * ga.y + vb[g].y * ib * gb.y,
+                          va[g].z * ia * ga.z + vb[g].z * ib * gb.z, va[g].w * ia * ga.w + vb[g].w * ib * gb.w));
+    }
+  }
+}
+
 bool dt_ok(int d) { return d == HB_DTYPE_F32 || d == HB_DTYPE_BF16; }
 
 }  // namespace
@@ -127,8 +230,24 @@ extern "C" int hb_canon_conv(const float* h, const float* taps_a, const float* t
   if (n_tokens == 0) return HB_OK;
   int per = (width + 255) / 256;
   if (per > 32) per = 32;
-  canon_conv_kernel<<<dim3(n_tokens, per), 256, 0, stream>>>(h, taps_a, taps_b, state, state_stride, cu_seqlens,
-                                                            seq_of_token, slots, out_a, out_b, dtype, width, taps_n);
+  auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  const bool vec = width % 4 == 0 && state_stride % 4 == 0 && taps_n <= 4 && (width / 4 + 127) / 128 <= 65535 &&
+                   aligned16(h) && aligned16(state) && aligned16(taps_a) && aligned16(taps_b) && aligned16(out_a) &&
+                   aligned16(out_b);
+  if (vec) {
+    const dim3 grid(n_tokens, (width / 4 + 127) / 128);
+#define HB_CANON_VEC(K)                                                                                          \
+    canon_conv_vec_kernel<K><<<grid, 128, 0, stream>>>(h, taps_a, taps_b, state, state_stride, cu_seqlens, seq_of_token, \
+                                                       slots, out_a, out_b, dtype, width)
+    if (taps_n == 1) HB_CANON_VEC(1);
+    else if (taps_n == 2) HB_CANON_VEC(2);
+    else if (taps_n == 3) HB_CANON_VEC(3);
+    else HB_CANON_VEC(4);
+#undef HB_CANON_VEC
+  } else {
+    canon_conv_kernel<<<dim3(n_tokens, per), 256, 0, stream>>>(h, taps_a, taps_b, state, state_stride, cu_seqlens,
+                                                              seq_of_token, slots, out_a, out_b, dtype, width, taps_n);
+  }
   HB_LAUNCH_CHECK();
   if (update_state && taps_n > 1 && n_seqs > 0) {
     canon_tail_kernel<<<dim3(n_seqs, per), 256, 0, stream>>>(h, state, state_stride, cu_seqlens, slots, width, taps_n);
@@ -154,8 +273,19 @@ extern "C" int hb_rmsnorm_mean2(const void* a, const void* b, int in_dtype, cons
   if (!a || !b || !wa || !wb || !out || rows < 0 || width <= 0 || !dt_ok(in_dtype) || !dt_ok(w_dtype) || !dt_ok(out_dtype))
     return HB_ERR_BAD_ARG;
   if (rows == 0) return HB_OK;
-  const int threads = width >= 2048 ? 512 : 256;
-  rmsnorm_mean2_kernel<<<rows, threads, 0, stream>>>(a, b, in_dtype, wa, wb, w_dtype, eps, out, out_dtype, width);
+  auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (width % 4 == 0 && width <= 4 * 4 * 256 && aligned16(a) && aligned16(b) && aligned16(wa) && aligned16(wb) && aligned16(out)) {
+    // whole warps, about two groups of four channels a thread
+    int threads = ((width / 8 + 31) / 32) * 32;
+    threads = threads < 32 ? 32 : (threads > 256 ? 256 : threads);
+    if (width <= 4 * 2 * threads)
+      rmsnorm_mean2_vec_kernel<2><<<rows, threads, 0, stream>>>(a, b, in_dtype, wa, wb, w_dtype, eps, out, out_dtype, width);
+    else
+      rmsnorm_mean2_vec_kernel<4><<<rows, threads, 0, stream>>>(a, b, in_dtype, wa, wb, w_dtype, eps, out, out_dtype, width);
+  } else {
+    const int threads = width >= 2048 ? 512 : 256;
+    rmsnorm_mean2_kernel<<<rows, threads, 0, stream>>>(a, b, in_dtype, wa, wb, w_dtype, eps, out, out_dtype, width);
+  }
   HB_LAUNCH_CHECK();
   return HB_OK;
 }

@@ -955,9 +955,15 @@ def _decode_splits(longest: int, groups: int) -> Tuple[int, int]:
     return best[2], best[1]
 
 
+# Row lengths (head dims) of the tensor-core attention kernels. 192 is a latent of 128 with a rotated key part of 64;
+# only the cp.async decode kernel, the mma.sync prefill kernel and the tcgen05 prefill kernel take it (the TMA
+# decode kernels answer "unsupported" and the callers fall back to those).
+TC_ROW_LENGTHS = (64, 128, 192)
+
+
 def decode_attention_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int) -> bool:
     """Shapes the tensor-core decode kernel takes; anything else goes to the general kernel."""
-    return q_dtype == torch.bfloat16 and hd in (64, 128) and nh % nkv == 0 and nh // nkv <= 16
+    return q_dtype == torch.bfloat16 and hd in TC_ROW_LENGTHS and nh % nkv == 0 and nh // nkv <= 16
 
 
 def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
@@ -1085,7 +1091,7 @@ def decode_attention_fused(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positi
 
 def prefill_attention_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int) -> bool:
     """Shapes the tensor-core prefill kernel takes; anything else goes to the general kernel."""
-    return q_dtype == torch.bfloat16 and hd in (64, 128) and nh % nkv == 0
+    return q_dtype == torch.bfloat16 and hd in TC_ROW_LENGTHS and nh % nkv == 0
 
 
 def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
@@ -1121,9 +1127,9 @@ PREFILL_TC_MIN_TOKENS = 128     # a request needs at least a tile of new tokens 
 
 
 def prefill_attention_tc_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int, page_size: int) -> bool:
-    """Shapes the tcgen05 prefill kernel takes: bfloat16, head_dim 64 or 128, pages of 16, 32 or a
+    """Shapes the tcgen05 prefill kernel takes: bfloat16, head_dim 64, 128 or 192, pages of 16, 32 or a
     multiple of 64 positions (a 64-key tile is loaded page by page with TMA)."""
-    return q_dtype == torch.bfloat16 and hd in (64, 128) and nh % nkv == 0 and page_size % 16 == 0 and \
+    return q_dtype == torch.bfloat16 and hd in TC_ROW_LENGTHS and nh % nkv == 0 and page_size % 16 == 0 and \
         (64 % page_size == 0 or page_size % 64 == 0)
 
 

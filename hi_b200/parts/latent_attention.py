@@ -24,7 +24,7 @@ class LatentAttentionMixer(Part):
     the step's queries are mapped into latent space (one batched product), attention runs over the paged
     latents with one shared "kv head" whose keys and values are the same rows (the paged attention kernels
     of the other mixers), and the result is mapped out by V_a (another batched product). The cached rows are
-    padded to a multiple of 16 elements with zeros, which changes no dot product.
+    padded with zeros to 64, 128 or 192 elements (longer ones to a multiple of 16), which changes no dot product.
 
     A mixer with ``kv_source`` makes no latents: its schedule entry reads the cache slot of the layer that
     does (``writes_cache=False``), with its own U, V, queries and everything else.
@@ -65,7 +65,9 @@ class LatentAttentionMixer(Part):
         if self.rot % 2:
             raise ValueError(f"{prefix}: rot_dim {self.rot} must be even")
         self.qdim = self.dim + self.rot                          # a query head as the checkpoint has it
-        self.row_len = -(-(self.rank + self.rot) // 16) * 16
+        # the cached row: padded with zeros to a length the tensor-core kernels take (64, 128, 192), else to 16s
+        need = self.rank + self.rot
+        self.row_len = next((n for n in ops.TC_ROW_LENGTHS if need <= n), -(-need // 16) * 16)
         if self.row_len > 512:
             raise ValueError(f"{prefix}: kv_rank {self.rank} + rot_dim {self.rot} is not supported (up to 512)")
         self._freq_host = None

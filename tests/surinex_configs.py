@@ -82,8 +82,14 @@ SX_E = config(77, 50, 1e-5, 5, [
     latent(2, 6, 10, 14, 18, 7, 0.4, 10000.0, mlp=dense(22)),
     gla(3, 18, 10, 12.0, rank=9),
 ], loop=(0, 1, 4))
+# a latent row between 128 and 192 (the longest the tensor-core attention kernels take) under twenty heads, more
+# than one call of the decode kernel packs; no loop
+SX_F = config(150, 64, 1e-5, 2, [
+    latent(20, 8, 40, 8, 144, 24, 0.2, 10000.0, mlp=dense(64)),
+    gla(2, 16, 16, 4.0, rank=4),
+])
 
-CONFIGS = {"A": SX_A, "B": SX_B, "C": SX_C, "D": SX_D, "E": SX_E}
+CONFIGS = {"A": SX_A, "B": SX_B, "C": SX_C, "D": SX_D, "E": SX_E, "F": SX_F}
 
 
 def peaked(cfg: dict, factor: float) -> dict:

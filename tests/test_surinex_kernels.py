@@ -45,7 +45,7 @@ def turn(x, pos, freqs, interleaved, sign=1.0):
 
 
 # --------------------------------------------------------------------------- the block's convolutions
-@pytest.mark.parametrize("width,taps", [(40, 4), (64, 1), (50, 8), (1030, 2)])
+@pytest.mark.parametrize("width,taps", [(40, 4), (64, 1), (36, 3), (2052, 2), (50, 8), (1030, 2), (24, 5)])
 @pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-6), (torch.bfloat16, 8e-3)])
 def test_canon_conv_carries_rows_between_portions(width, taps, dt, tol):
     """Two requests cut into portions of many sizes (shorter than the taps too) in changing company, on slots 3
@@ -103,6 +103,15 @@ def test_stream_add_and_normed_mean():
     a, b = 3.0 * d1, 0.01 * d2
     close(ops.rmsnorm_mean2(a.to(DEV), b.to(DEV), wa.to(DEV), wb.to(DEV), 1e-5, torch.float32),
           0.5 * (norm(a, wa) + norm(b, wb)), 2e-6, "mean of two norms")
+    # widths that the four-channels-a-thread kernel takes (two or four groups a thread) and one beyond it
+    for w2 in (8, 72, 2048, 3000, 4100):
+        a, b = 3.0 * rnd(5, w2, seed=w2), 0.01 * rnd(5, w2, seed=w2 + 1)
+        wa2, wb2 = 1 + 0.3 * rnd(w2, seed=6), 1 + 0.3 * rnd(w2, seed=7)
+        close(ops.rmsnorm_mean2(a.to(DEV), b.to(DEV), wa2.to(DEV), wb2.to(DEV), 1e-5, torch.float32),
+              0.5 * (norm(a, wa2) + norm(b, wb2)), 2e-6, f"mean of two norms, width {w2}")
+        ab, bb = a.bfloat16(), b.bfloat16()
+        close(ops.rmsnorm_mean2(ab.to(DEV), bb.to(DEV), wa2.bfloat16().to(DEV), wb2.bfloat16().to(DEV), 1e-5, torch.bfloat16),
+              0.5 * (norm(ab, wa2.bfloat16()) + norm(bb, wb2.bfloat16())), 8e-3, f"bfloat16, width {w2}")
     wide = rnd(n, 200, seed=8)
     close(ops.rmsnorm_rows(wide.to(DEV)[:, 30:100], wa.to(DEV), 1e-5), norm(wide[:, 30:100], wa), 2e-6, "rows of a slice")
 
@@ -208,9 +217,9 @@ def test_sigmoid_attention_over_pages(dt, tol, nh, nkv, hd, vdim):
 
 
 @pytest.mark.parametrize("page", [16, 64])
-@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (8, 2, 128), (16, 1, 128)])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (8, 2, 128), (16, 1, 128), (6, 2, 192)])
 def test_sigmoid_attention_on_the_tensor_cores(nh, nkv, hd, page):
-    """bfloat16 heads of 64 and 128: single tokens of three requests at different depths through the decode kernel
+    """bfloat16 heads of 64, 128 and 192: single tokens of three requests at different depths through the decode kernel
     (keys cut into splits), and portions of 130 to 300 new tokens at the start and far into a context through the
     tcgen05 kernel, one request bringing a single token beside them; all against the plain sum."""
     from hi_b200.kernels import ops
@@ -257,6 +266,74 @@ def test_sigmoid_attention_on_the_tensor_cores(nh, nkv, hd, page):
 
 
 # --------------------------------------------------------------------------- recurrences
+@pytest.mark.parametrize("page", [16, 64])
+@pytest.mark.parametrize("nh,sliding", [(5, 0), (20, 0), (16, 150)])
+def test_softmax_over_shared_rows_of_192(nh, sliding, page):
+    """What latent attention with a rotated key part asks of the paged kernels in bfloat16: rows of 192 that are keys
+    and values at once, one kv head under many query heads. Single tokens (the decode kernel, sixteen heads a call),
+    portions of 2 to 70 tokens (mma.sync) and of 130 to 280 (tcgen05, with and without key splits), whole and far
+    into a context, with a sliding window too; one row's first 8 numbers are made large so that the query that
+    matches it puts nearly all its weight there (a row lost or shifted by one then shows)."""
+    from hi_b200.kernels import ops
+
+    hd, dt, scale = 192, torch.bfloat16, 0.09
+    g = torch.Generator().manual_seed(nh + page + sliding)
+    lens = (700, 281, 66)
+    per = -(-max(lens) // page)
+    perm = torch.randperm(3 * per + 3, generator=g)[: 3 * per].view(3, per)
+    pool = torch.zeros((3 * per + 3, 1, page, hd), dtype=dt, device=DEV)
+    rows = []
+    for r, n in enumerate(lens):
+        c = torch.randn(n, hd, generator=g).to(dt)
+        c[n // 3, :8] = 6.0
+        rows.append(c.float())
+        for p in range(n):
+            pool[perm[r, p // page], 0, p % page] = c[p].to(DEV)
+    table = perm.to(torch.int32).to(DEV)
+
+    def plain(q, c, start):
+        out = torch.zeros(q.shape[0], nh, hd, dtype=torch.float64)
+        for i in range(q.shape[0]):
+            p = start + i
+            lo = max(0, p - sliding + 1) if sliding else 0
+            keys = c[lo: p + 1].double()
+            w = torch.softmax(q[i].double() @ keys.T * scale, dim=-1)
+            out[i] = w @ keys
+        return out
+
+    def queries(n):
+        q = torch.randn(n, nh, hd, generator=g).to(dt)
+        q[:, 0, :8] = 4.0                                    # head 0 asks for the planted row
+        return q
+
+    # single tokens: the last position of every request
+    q = queries(3)
+    got = torch.empty_like(q, device=DEV)
+    for first in range(0, nh, 16):
+        part = q[:, first: first + 16].contiguous().to(DEV)
+        got[:, first: first + 16] = ops.decode_attention(part, pool, pool, table, i32([0, 1, 2]), i32([n - 1 for n in lens]),
+                                                         0, sliding, scale, max(lens))
+    for r, n in enumerate(lens):
+        close(got[r: r + 1], plain(q[r: r + 1].float(), rows[r], n - 1), 2e-2, f"single token of request {r}")
+    # portions
+    for news in (((420, 280), (0, 130), (64, 2)), ((630, 70), (279, 2), (0, 66))):
+        qs = [queries(n) for _s, n in news]
+        cu = [0]
+        for _s, n in news:
+            cu.append(cu[-1] + n)
+        pos = [p for s0, n in news for p in range(s0, s0 + n)]
+        longest = max(n for _s, n in news)
+        args = (torch.cat(qs).to(DEV), pool, pool, table, i32(cu), i32(pos), 3, longest, 0, sliding, scale)
+        runs = [("mma.sync", ops.prefill_attention(*args))]
+        if longest >= ops.PREFILL_TC_MIN_TOKENS:
+            runs += [(f"tcgen05, {k} splits", ops.prefill_attention_tc(*args, key_splits=k)) for k in (1, 3)]
+        for what, got in runs:
+            for r, (s0, n) in enumerate(news):
+                close(got[cu[r]: cu[r + 1]], plain(qs[r].float(), rows[r], s0), 2e-2, f"{what}: portion of request {r}")
+    torch.cuda.synchronize()
+    ops.check_tc_status()
+
+
 @pytest.mark.parametrize("heads,dim,vdim,general", [(2, 16, 24, False), (3, 5, 7, False), (1, 136, 20, False), (2, 48, 32, True)])
 def test_gated_linear_attention_inputs_and_recurrence(heads, dim, vdim, general):
     """gla_prep (scaled q, decay = sigmoid(z + b)^(1/tau)) and the recurrence without the delta rule's correction, two

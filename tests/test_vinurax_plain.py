@@ -82,7 +82,7 @@ def test_config_reader_and_spec():
     spec = arch.build_spec(cfg)
     assert [(e.cache, e.writes_cache) for e in spec.schedule] == [(0, True), (1, True), (1, False), (3, True), (4, True)]
     model = Model(spec, torch.bfloat16, "cpu")
-    assert model.cache_specs[1].head_dim == 64 and not model.cache_specs[1].values and model.cache_specs[4].head_dim == 48
+    assert model.cache_specs[1].head_dim == 64 and not model.cache_specs[1].values and model.cache_specs[4].head_dim == 64
     assert model.cache_specs[0].state_shape == (4 * 16 * 24 + 3 * (2 * 2 * 16 + 4 * 24),)
     for bad, word in (({**VX_A, "layers": [latent(2, 8, 8, 16, 0.1, kv_from=0)]}, "kv_from"),
                       ({**VX_A, "layers": [delta(3, 2, 8, 8, 2)]}, "kv_heads"),
