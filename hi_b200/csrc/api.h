@@ -78,6 +78,13 @@ int hb_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pa
                             int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd, int page_size, int chunk,
                             int window, float scale, int skip_single, int sink, const float* head_bias, int key_splits,
                             float* part_acc, float* part_ml, int* status, cudaStream_t stream);   // sink == 2 as above
+// sigmoid weights, one block per (query tile, head) over all its keys: the block turns its rows back by their
+// positions (values cached rotated: v_inv_freq [v_pairs] or null) and writes `out` (bfloat16) itself
+int hb_sigmoid_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                          int table_stride, const int* cu_seqlens, const int* positions, void* out, int n_tokens,
+                          int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd, int page_size, int chunk,
+                          int window, float scale, int skip_single, const float* head_bias, const float* v_inv_freq,
+                          int v_pairs, int v_interleaved, int* status, cudaStream_t stream);
 
 // mode: bit 0 = scores are the softmax over all experts (clear: the sigmoid of the chosen logit),
 // bit 1 = the chosen scores are divided by their sum; bits 8-15 = G, 16-23 = KEEP: only experts of the KEEP best

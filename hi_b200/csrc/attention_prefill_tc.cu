@@ -58,6 +58,11 @@ struct Args {
   // bias * log2 e)); nothing is normalised; every block leaves its plain sums in part_acc (zero-filled by the
   // caller, also with key_splits == 1) and the caller adds the splits.
   const float* head_bias;
+  // turn_inside (sigmoid weights, key_splits == 1): the block turns its rows back itself and writes `out`. The
+  // values were cached rotated by their own positions: pair m of the row's first 2 * v_pairs dims (interleaved:
+  // dims 2m, 2m + 1; else m, m + v_pairs with 2 * v_pairs == head_dim) turns by -position * v_inv_freq[m].
+  int turn_inside, v_pairs, v_interleaved;
+  const float* v_inv_freq;
 };
 
 template <int HD>
@@ -399,7 +404,64 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) atomicExch(a.status, 18);
       } else {
         tc::fence_after();
-        if (a.key_splits > 1 || sigmoid) {
+        if (sigmoid && a.turn_inside) {
+          // the plain sum is the result: turned back by the row's position in float32, rounded once
+          __nv_bfloat16* dst = a.out + ((size_t)(tok0 + r) * a.nh + h) * HD;
+          const float fpos = (float)pos;
+          auto store32 = [&](const float* o, int c) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 pack;
+              uint32_t* w = reinterpret_cast<uint32_t*>(&pack);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 hh = __floats2bfloat162_rn(o[i + 2 * e], o[i + 2 * e + 1]);
+                w[e] = *reinterpret_cast<uint32_t*>(&hh);
+              }
+              *reinterpret_cast<uint4*>(dst + c + i) = pack;
+            }
+          };
+          if (a.v_interleaved || a.v_pairs == 0) {
+#pragma unroll 1
+            for (int c = 0; c < HD; c += 32) {
+              float o[32];
+              tc::ld32(tmem_o + lane_addr + c, o);
+              if (row_ok) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                  const int mth = c / 2 + e;
+                  if (mth < a.v_pairs) {
+                    float sn, cs;
+                    sincosf(fpos * a.v_inv_freq[mth], &sn, &cs);
+                    const float u = o[2 * e], v = o[2 * e + 1];
+                    o[2 * e] = u * cs + v * sn;
+                    o[2 * e + 1] = v * cs - u * sn;
+                  }
+                }
+                store32(o, c);
+              }
+            }
+          } else {
+#pragma unroll 1
+            for (int c = 0; c < HD / 2; c += 32) {
+              float lo[32], hi[32];
+              tc::ld32(tmem_o + lane_addr + c, lo);
+              tc::ld32(tmem_o + lane_addr + HD / 2 + c, hi);
+              if (row_ok) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  float sn, cs;
+                  sincosf(fpos * a.v_inv_freq[c + i], &sn, &cs);
+                  const float u = lo[i], v = hi[i];
+                  lo[i] = u * cs + v * sn;
+                  hi[i] = v * cs - u * sn;
+                }
+                store32(lo, c);
+                store32(hi, HD / 2 + c);
+              }
+            }
+          }
+        } else if (a.key_splits > 1 || sigmoid) {
           // this share of the keys only: the row as it is, with its max and sum, for the merge
           const size_t at = ((size_t)(tok0 + r) * a.nh + h) * a.key_splits + piece;
           if (row_ok && !sigmoid) {
@@ -478,26 +540,64 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const Args& 
 // then go unnormalised to `part_acc` [n_tokens * nh][key_splits][hd] and `part_ml`
 // [n_tokens * nh][key_splits][2] for hb_attention_merge, and `out` is not written), and `status` (one int on the device, zero before the call; nonzero afterwards = a wait
 // timed out). HB_ERR_UNSUPPORTED for other shapes: the caller uses hb_attention_prefill.
+namespace {
+int prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
+               const int* cu_seqlens, const int* positions, void* out, int n_tokens, int n_pages, int n_seqs, int max_new,
+               int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int skip_single, int sink,
+               const float* head_bias, int key_splits, float* part_acc, float* part_ml, int* status, int turn_inside,
+               const float* v_inv_freq, int v_pairs, int v_interleaved, cudaStream_t stream);
+}  // namespace
+
 extern "C" int hb_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                        int table_stride, const int* cu_seqlens, const int* positions, void* out,
                                        int n_tokens, int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd,
                                        int page_size, int chunk, int window, float scale, int skip_single,
                                        int sink, const float* head_bias, int key_splits, float* part_acc,
                                        float* part_ml, int* status, cudaStream_t stream) {
+  return prefill_tc(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_tokens, n_pages, n_seqs,
+                    max_new, nh, nkv, hd, page_size, chunk, window, scale, skip_single, sink, head_bias, key_splits,
+                    part_acc, part_ml, status, 0, nullptr, 0, 0, stream);
+}
+
+// Sigmoid weights with the result written by the kernel itself: `out` [n_tokens, nh, hd] bfloat16 takes every
+// row's plain sum over ALL its keys, turned back by the row's position when the values are cached rotated
+// (`v_inv_freq` [v_pairs] or null; without `v_interleaved` the pairs are (m, m + hd / 2) and v_pairs == hd / 2).
+// Rows of requests that `skip_single` leaves out are not written.
+extern "C" int hb_sigmoid_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                     int table_stride, const int* cu_seqlens, const int* positions, void* out,
+                                     int n_tokens, int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd,
+                                     int page_size, int chunk, int window, float scale, int skip_single,
+                                     const float* head_bias, const float* v_inv_freq, int v_pairs, int v_interleaved,
+                                     int* status, cudaStream_t stream) {
+  if (v_pairs < 0 || (v_pairs > 0 && !v_inv_freq) || 2 * v_pairs > hd) return HB_ERR_BAD_ARG;
+  if (v_pairs > 0 && !v_interleaved && 2 * v_pairs != hd) return HB_ERR_UNSUPPORTED;
+  return prefill_tc(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_tokens, n_pages, n_seqs,
+                    max_new, nh, nkv, hd, page_size, chunk, window, scale, skip_single, 2, head_bias, 1, nullptr, nullptr,
+                    status, 1, v_inv_freq, v_pairs, v_interleaved, stream);
+}
+
+namespace {
+int prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
+               const int* cu_seqlens, const int* positions, void* out, int n_tokens, int n_pages, int n_seqs, int max_new,
+               int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int skip_single, int sink,
+               const float* head_bias, int key_splits, float* part_acc, float* part_ml, int* status, int turn_inside,
+               const float* v_inv_freq, int v_pairs, int v_interleaved, cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !cu_seqlens || !positions || !out || !status) return HB_ERR_BAD_ARG;
   if (n_tokens < 0 || n_pages <= 0 || n_seqs < 0 || max_new < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 ||
       page_size <= 0 || table_stride <= 0 || chunk < 0 || window < 0 || key_splits < 1 || key_splits > 64 ||
-      (sink == 2 ? !part_acc : (key_splits > 1 && (!part_acc || !part_ml))))
+      (sink == 2 && !turn_inside ? !part_acc : (key_splits > 1 && (!part_acc || !part_ml))))
     return HB_ERR_BAD_ARG;
   if (page_size % 16 != 0 || !(BKEYS % page_size == 0 || page_size % BKEYS == 0)) return HB_ERR_UNSUPPORTED;
   if (n_seqs > 65535 || nh > 65535) return HB_ERR_UNSUPPORTED;
   if (!(scale > 0.f)) return HB_ERR_UNSUPPORTED;       // the largest raw score is taken for the largest scaled one
   if (n_seqs == 0 || max_new == 0 || n_tokens == 0) return HB_OK;
   Args a{block_table, cu_seqlens, positions, (__nv_bfloat16*)out, status, table_stride, nh, nkv, page_size, chunk,
-         window, skip_single, page_size < BKEYS ? page_size : BKEYS, scale * 1.4426950408889634f, key_splits, part_acc, part_ml, sink, head_bias};
+         window, skip_single, page_size < BKEYS ? page_size : BKEYS, scale * 1.4426950408889634f, key_splits, part_acc, part_ml, sink, head_bias,
+         turn_inside, v_pairs, v_interleaved, v_inv_freq};
   const long long pool_rows = (long long)n_pages * nkv * page_size;
   if (hd == 192) return launch<192>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
   if (hd == 128) return launch<128>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
   if (hd == 64) return launch<64>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
   return HB_ERR_UNSUPPORTED;
 }
+}  // namespace

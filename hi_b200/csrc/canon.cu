@@ -62,32 +62,29 @@ __global__ void canon_conv_kernel(const float* __restrict__ h, const float* __re
   }
 }
 
-// The same with four channels a thread (width a multiple of 4): rows of h and the taps of four neighbouring
-// channels ([4][K] floats, contiguous) come as 16-byte loads, results leave as 8- or 16-byte stores.
-template <int K>
+// The same with four channels a thread (width a multiple of 4) and kTokensPerThread consecutive rows of the step a
+// thread: the taps of its four channels ([4][K] floats, contiguous) are read once into registers, a request's rows
+// slide through a window of K float4 (one new 16-byte load a row; after a request's first row of the run, or
+// where the next row belongs to another request, the window is filled anew, rows before the portion from the
+// state), results leave as 8- or 16-byte stores. Steps of few rows take one row a thread.
+template <int K, int kTokensPerThread>
 __global__ void canon_conv_vec_kernel(const float* __restrict__ h, const float* __restrict__ taps_a,
                                       const float* __restrict__ taps_b, const float* __restrict__ state,
                                       long long state_stride, const int* __restrict__ cu_seqlens,
                                       const int* __restrict__ seq_of_token, const int* __restrict__ slots,
-                                      void* __restrict__ out_a, void* __restrict__ out_b, int dtype, int width) {
-  const int t = blockIdx.x;
+                                      void* __restrict__ out_a, void* __restrict__ out_b, int dtype, int width,
+                                      int n_tokens) {
+  const int t0 = blockIdx.x * kTokensPerThread;
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
   if (c >= width) return;
-  const int s = seq_of_token[t];
-  const int start = cu_seqlens[s];
-  const int local = t - start;
-  const float* tail = state + (size_t)slots[s] * state_stride;      // [K-1, W]
-  float4 x[K];
+  float wa[4 * K], wb[4 * K];
 #pragma unroll
-  for (int j = 0; j < K; ++j) {
-    const int rel = local - (K - 1) + j;
-    x[j] = *reinterpret_cast<const float4*>(rel >= 0 ? h + (size_t)(start + rel) * width + c
-                                                     : tail + (size_t)(K - 1 + rel) * width + c);
+  for (int i = 0; i < K; ++i) {
+    *reinterpret_cast<float4*>(wa + 4 * i) = *reinterpret_cast<const float4*>(taps_a + (size_t)c * K + 4 * i);
+    *reinterpret_cast<float4*>(wb + 4 * i) = taps_b ? *reinterpret_cast<const float4*>(taps_b + (size_t)c * K + 4 * i)
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  auto run = [&](const float* taps, void* out) {
-    float w[4 * K];
-#pragma unroll
-    for (int i = 0; i < K; ++i) *reinterpret_cast<float4*>(w + 4 * i) = *reinterpret_cast<const float4*>(taps + (size_t)c * K + 4 * i);
+  auto emit = [&](const float* w, const float4 (&x)[K], void* out, int t) {
     float4 y = x[K - 1];
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
@@ -106,8 +103,32 @@ __global__ void canon_conv_vec_kernel(const float* __restrict__ h, const float* 
       *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)t * width + c) = pack;
     }
   };
-  run(taps_a, out_a);
-  if (taps_b) run(taps_b, out_b);
+  float4 x[K];
+  int prev_seq = -1;
+#pragma unroll 1
+  for (int i = 0; i < kTokensPerThread; ++i) {
+    const int t = t0 + i;
+    if (t >= n_tokens) break;
+    const int s = seq_of_token[t];
+    if (s == prev_seq) {                           // the next row of the same request: slide
+#pragma unroll
+      for (int j = 0; j + 1 < K; ++j) x[j] = x[j + 1];
+      x[K - 1] = *reinterpret_cast<const float4*>(h + (size_t)t * width + c);
+    } else {
+      const int start = cu_seqlens[s];
+      const int local = t - start;
+      const float* tail = state + (size_t)slots[s] * state_stride;      // [K-1, W]
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        const int rel = local - (K - 1) + j;
+        x[j] = *reinterpret_cast<const float4*>(rel >= 0 ? h + (size_t)(start + rel) * width + c
+                                                         : tail + (size_t)(K - 1 + rel) * width + c);
+      }
+      prev_seq = s;
+    }
+    emit(wa, x, out_a, t);
+    if (taps_b) emit(wb, x, out_b, t);
+  }
 }
 
 // The last K-1 rows of h of every request after this step's rows replace its state's.
@@ -235,10 +256,17 @@ extern "C" int hb_canon_conv(const float* h, const float* taps_a, const float* t
                    aligned16(h) && aligned16(state) && aligned16(taps_a) && aligned16(taps_b) && aligned16(out_a) &&
                    aligned16(out_b);
   if (vec) {
-    const dim3 grid(n_tokens, (width / 4 + 127) / 128);
+    const int per_thread = n_tokens >= 1024 ? 8 : 1;
+    const dim3 grid((n_tokens + per_thread - 1) / per_thread, (width / 4 + 127) / 128);
 #define HB_CANON_VEC(K)                                                                                          \
-    canon_conv_vec_kernel<K><<<grid, 128, 0, stream>>>(h, taps_a, taps_b, state, state_stride, cu_seqlens, seq_of_token, \
-                                                       slots, out_a, out_b, dtype, width)
+    do {                                                                                                         \
+      if (per_thread == 8)                                                                                       \
+        canon_conv_vec_kernel<K, 8><<<grid, 128, 0, stream>>>(h, taps_a, taps_b, state, state_stride, cu_seqlens, \
+                                                              seq_of_token, slots, out_a, out_b, dtype, width, n_tokens); \
+      else                                                                                                       \
+        canon_conv_vec_kernel<K, 1><<<grid, 128, 0, stream>>>(h, taps_a, taps_b, state, state_stride, cu_seqlens, \
+                                                              seq_of_token, slots, out_a, out_b, dtype, width, n_tokens); \
+    } while (0)
     if (taps_n == 1) HB_CANON_VEC(1);
     else if (taps_n == 2) HB_CANON_VEC(2);
     else if (taps_n == 3) HB_CANON_VEC(3);

@@ -33,6 +33,7 @@ _SIGNATURES = {
     "hb_attention_decode_fused": [P, P, I, I, I, F, I, F, F, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P, P, I, F, I, P],
     "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
     "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P, I, P, P, P, P],
+    "hb_sigmoid_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P, I, I, P, P],
     "hb_sigmoid_merge": [P, P, P, I, I, P, I, I, I, I, I, P],
     "hb_router_topk": [P, I, P, I, I, I, I, I, I, F, P, P, P, P],
     "hb_moe_plan": [P, I, I, P, P, P, P, P],
@@ -913,8 +914,9 @@ def sigmoid_prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages
                                  window: int, scale: float, head_bias: torch.Tensor, skip_single: bool = False,
                                  v_inv_freq: Optional[torch.Tensor] = None, v_interleaved: bool = False) -> torch.Tensor:
     """:func:`sigmoid_attention` for portions of prompts in bfloat16 on tcgen05: the kernel of
-    :func:`prefill_attention_tc` with sigmoid weights; its rows leave as float32 sums and :func:`sigmoid_merge` turns
-    them back. Rows of requests that bring one token are zero with ``skip_single``."""
+    :func:`prefill_attention_tc` with sigmoid weights, which turns its rows back by their positions in its epilogue
+    (pairs in halves over a part of the row only: float32 sums out and :func:`sigmoid_merge`). Rows of requests
+    that bring one token are zero with ``skip_single``."""
     _need(q, "q", torch.bfloat16); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
     _need(head_bias, "head_bias", torch.float32)
     for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (positions, "positions")):
@@ -927,6 +929,20 @@ def sigmoid_prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages
         raise KernelError(f"tcgen05 prefill attention does not take nh={nh} nkv={nkv} head_dim={hd} page={page_size}")
     if cu_seqlens.numel() != n_seqs + 1 or block_table.shape[0] < n_seqs:
         raise KernelError("cu_seqlens / block_table do not match the number of requests")
+    v_pairs = 0
+    if v_inv_freq is not None:
+        _need(v_inv_freq, "v_inv_freq", torch.float32)
+        v_pairs = v_inv_freq.numel()
+    if v_pairs == 0 or v_interleaved or 2 * v_pairs == hd:
+        # the kernel turns its rows back itself and writes the result
+        out = torch.zeros_like(q) if skip_single else torch.empty_like(q)
+        _check(lib().hb_sigmoid_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                                           _ptr(cu_seqlens), _ptr(positions), _ptr(out), n, n_pages, n_seqs, int(max_new), nh,
+                                           nkv, hd, page_size, int(chunk), int(window), float(scale), int(skip_single),
+                                           _ptr(head_bias), _ptr(v_inv_freq), v_pairs, int(v_interleaved),
+                                           _ptr(_tc_status(q.device)), _stream()), "sigmoid_prefill_tc")
+        TC_USED[0] = True
+        return out
     part_acc = torch.zeros((n, nh, 1, hd), dtype=torch.float32, device=q.device)
     _check(lib().hb_attention_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                                          block_table.shape[1], _ptr(cu_seqlens), _ptr(positions), _ptr(part_acc), n, n_pages,

@@ -86,6 +86,35 @@ def test_canon_conv_carries_rows_between_portions(width, taps, dt, tol):
     assert float(state[0].min()) == 7.0 and float(state[2].min()) == 7.0       # other slots are not touched
 
 
+@pytest.mark.parametrize("width,taps", [(64, 4), (36, 3), (8, 2)])
+def test_canon_conv_of_a_long_step(width, taps):
+    """Steps of more than a thousand rows (several rows a thread, a request's rows sliding through registers): three
+    requests of unequal length side by side whose borders fall inside a thread's run of rows, then their next portions
+    in a second such step; the state carries the rows between the two."""
+    from hi_b200.kernels import ops
+
+    lens = (1203, 7, 1001)
+    hs = [rnd(n, width, seed=11 + i) for i, n in enumerate(lens)]
+    ta, tb = rnd(width, taps, seed=3, scale=0.5), rnd(width, taps, seed=4, scale=0.5)
+    state = torch.zeros((3, (taps - 1) * width), device=DEV)
+    got_a, got_b = [[], [], []], [[], [], []]
+    for ns, starts in (((601, 3, 499), (0, 0, 0)), ((602, 4, 502), (601, 3, 499))):
+        h = torch.cat([hs[i][starts[i]: starts[i] + ns[i]] for i in range(3)]).to(DEV)
+        cu = [0, ns[0], ns[0] + ns[1], sum(ns)]
+        sot = [i for i in range(3) for _ in range(ns[i])]
+        ya, yb = ops.canon_conv(h, ta.to(DEV), tb.to(DEV), state, i32(cu), i32(sot), i32([2, 0, 1]), torch.float32)
+        for i in range(3):
+            got_a[i].append(ya[cu[i]: cu[i + 1]])
+            got_b[i].append(yb[cu[i]: cu[i + 1]])
+    for i in range(3):
+        for got, t in ((got_a, ta), (got_b, tb)):
+            y = hs[i].double().clone()
+            for j in range(taps):
+                shift = taps - 1 - j
+                y[shift:] += t[:, j].double() * hs[i][: lens[i] - shift].double()
+            close(torch.cat(got[i]), y, 1e-6, f"request {i}")
+
+
 def test_stream_add_and_normed_mean():
     from hi_b200.kernels import ops
 
