@@ -140,8 +140,8 @@ class SurinexConfig:
             raise ConfigError("config.json: 'vocab' and 'width' must be positive")
         eps = need(obj(raw, "norm", "norm"), "eps", float, "norm")
         taps = need(obj(raw, "canon", "canon"), "taps", int, "canon")
-        if not 1 <= taps <= 8:
-            raise ConfigError("config.json: 'canon.taps' must lie in 1..8")
+        if taps < 1:
+            raise ConfigError("config.json: 'canon.taps' must be at least 1")
         entries = raw.get("layers")
         if not isinstance(entries, list) or not entries:
             raise ConfigError("config.json: 'layers' must be a non-empty list")

@@ -26,8 +26,6 @@ __device__ __forceinline__ void st_any(void* p, int dtype, size_t i, float v) {
   else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
 }
 
-constexpr int kMaxTaps = 8;
-
 // grid (tokens, channel groups); a thread per channel.
 __global__ void canon_conv_kernel(const float* __restrict__ h, const float* __restrict__ taps_a,
                                   const float* __restrict__ taps_b, const float* __restrict__ state,
@@ -40,22 +38,13 @@ __global__ void canon_conv_kernel(const float* __restrict__ h, const float* __re
   const int local = t - start;
   const float* tail = state + (size_t)slots[s] * state_stride;      // [K-1, W]
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
-    float x[kMaxTaps];
-#pragma unroll
-    for (int j = 0; j < kMaxTaps; ++j) {
-      if (j < K) {
-        const int rel = local - (K - 1) + j;
-        x[j] = rel >= 0 ? h[(size_t)(start + rel) * width + c] : tail[(size_t)(K - 1 + rel) * width + c];
-      }
-    }
-    const float own = x[K - 1];
-    float a = 0.f, b = 0.f;
-#pragma unroll
-    for (int j = 0; j < kMaxTaps; ++j) {
-      if (j < K) {
-        a = fmaf(taps_a[(size_t)c * K + j], x[j], a);
-        if (taps_b) b = fmaf(taps_b[(size_t)c * K + j], x[j], b);
-      }
+    float own = 0.f, a = 0.f, b = 0.f;
+    for (int j = 0; j < K; ++j) {
+      const int rel = local - (K - 1) + j;
+      const float x = rel >= 0 ? h[(size_t)(start + rel) * width + c] : tail[(size_t)(K - 1 + rel) * width + c];
+      own = x;                                     // the last tap's row is the token's own
+      a = fmaf(taps_a[(size_t)c * K + j], x, a);
+      if (taps_b) b = fmaf(taps_b[(size_t)c * K + j], x, b);
     }
     st_any(out_a, dtype, (size_t)t * width + c, own + a);
     if (taps_b) st_any(out_b, dtype, (size_t)t * width + c, own + b);
@@ -247,7 +236,6 @@ extern "C" int hb_canon_conv(const float* h, const float* taps_a, const float* t
     return HB_ERR_BAD_ARG;
   if (width <= 0 || taps_n < 1 || n_tokens < 0 || n_seqs < 0 || state_stride < (long long)(taps_n - 1) * width)
     return HB_ERR_BAD_ARG;
-  if (taps_n > kMaxTaps) return HB_ERR_UNSUPPORTED;
   if (n_tokens == 0) return HB_OK;
   int per = (width + 255) / 256;
   if (per > 32) per = 32;

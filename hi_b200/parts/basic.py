@@ -545,8 +545,8 @@ class ParallelConvBlock(Part):
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
         self.width, self.taps = int(params["hidden_size"]), int(params["taps"])
-        if not 1 <= self.taps <= 8:
-            raise ValueError(f"{prefix}: {self.taps} taps are not supported (1 to 8)")
+        if self.taps < 1:
+            raise ValueError(f"{prefix}: a convolution has at least one tap, not {self.taps}")
         self.has_ff = bool(params.get("feed_forward", True))
         self.taps_a = self.taps_b = self._no_state = None
 

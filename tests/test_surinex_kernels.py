@@ -45,7 +45,7 @@ def turn(x, pos, freqs, interleaved, sign=1.0):
 
 
 # --------------------------------------------------------------------------- the block's convolutions
-@pytest.mark.parametrize("width,taps", [(40, 4), (64, 1), (36, 3), (2052, 2), (50, 8), (1030, 2), (24, 5)])
+@pytest.mark.parametrize("width,taps", [(40, 4), (64, 1), (36, 3), (2052, 2), (50, 8), (1030, 2), (24, 5), (28, 11)])
 @pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-6), (torch.bfloat16, 8e-3)])
 def test_canon_conv_carries_rows_between_portions(width, taps, dt, tol):
     """Two requests cut into portions of many sizes (shorter than the taps too) in changing company, on slots 3
