@@ -1072,8 +1072,9 @@ def case_surinex(width=2048, heads=16, ff=8192, layers=6, tokens=2048, batch=8, 
         row(what, "residual add of two results + RMSNorm, float32 out", ms, n * width * (4 + 2 + 2 + 4 + 4))
         ms = timed(lambda: ops.add_rmsnorm(x, d1, w, 1e-5, bf))
         row(what, "like: residual add + RMSNorm", ms, n * width * (4 + 2 + 4 + 2), "twice per layer there")
-        ms = timed(lambda: ops.canon_conv(h, ta, tb, cstate, cu, sot, slots, bf))
-        row(what, "two convolutions of the norm's output (4 taps) + state", ms, n * width * (4 + 2 + 2), "two launches")
+        ms = timed(lambda: ops.canon_conv(h, ta, tb, cstate, cu, sot, slots, bf, single_tokens=seqs == n))
+        row(what, "two convolutions of the norm's output (4 taps) + state", ms, n * width * (4 + 2 + 2),
+            "one launch" if seqs == n else "two launches")
         emb, vec = rnd(n, width, dt=f32), rnd(width, dt=f32)
         ms = timed(lambda: ops.stream_add(x, d1, d2, emb, vec))
         row(what, "between passes: stream += two results + embedding + vector", ms, n * width * (4 + 2 + 2 + 4 + 4))

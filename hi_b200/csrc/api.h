@@ -185,7 +185,9 @@ int hb_random_normal(void* out, int dtype, long long n, long long first, unsigne
                      cudaStream_t stream);
 
 // canon.cu: the norm's output through a short causal convolution over time per channel, kept float32 between the
-// two; what is added to the stream between passes over a range of layers; the mean of two normed mixer outputs
+// two; what is added to the stream between passes over a range of layers; the mean of two normed mixer outputs.
+// update_state: 0 the state stays, 1 a second launch stores the portions' last rows, 2 every request brings exactly
+// one row and the convolution kernel moves its state itself
 int hb_canon_conv(const float* h, const float* taps_a, const float* taps_b, float* state, long long state_stride,
                   const int* cu_seqlens, const int* seq_of_token, const int* slots, void* out_a, void* out_b, int dtype,
                   int n_tokens, int n_seqs, int width, int taps_n, int update_state, cudaStream_t stream);

@@ -28,21 +28,25 @@ __device__ __forceinline__ void st_any(void* p, int dtype, size_t i, float v) {
 
 // grid (tokens, channel groups); a thread per channel.
 __global__ void canon_conv_kernel(const float* __restrict__ h, const float* __restrict__ taps_a,
-                                  const float* __restrict__ taps_b, const float* __restrict__ state,
+                                  const float* __restrict__ taps_b, float* state,
                                   long long state_stride, const int* __restrict__ cu_seqlens,
                                   const int* __restrict__ seq_of_token, const int* __restrict__ slots,
-                                  void* __restrict__ out_a, void* __restrict__ out_b, int dtype, int width, int K) {
+                                  void* __restrict__ out_a, void* __restrict__ out_b, int dtype, int width, int K,
+                                  int fuse_tail) {
   const int t = blockIdx.x;
   const int s = seq_of_token[t];
   const int start = cu_seqlens[s];
   const int local = t - start;
   const float* tail = state + (size_t)slots[s] * state_stride;      // [K-1, W]
+  float* tail_w = state + (size_t)slots[s] * state_stride;
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
     float own = 0.f, a = 0.f, b = 0.f;
     for (int j = 0; j < K; ++j) {
       const int rel = local - (K - 1) + j;
       const float x = rel >= 0 ? h[(size_t)(start + rel) * width + c] : tail[(size_t)(K - 1 + rel) * width + c];
       own = x;                                     // the last tap's row is the token's own
+      // the request's only token of the step: its inputs move up a row in the state (row j - 1 is read no more)
+      if (fuse_tail && j >= 1) tail_w[(size_t)(j - 1) * width + c] = x;
       a = fmaf(taps_a[(size_t)c * K + j], x, a);
       if (taps_b) b = fmaf(taps_b[(size_t)c * K + j], x, b);
     }
@@ -58,11 +62,11 @@ __global__ void canon_conv_kernel(const float* __restrict__ h, const float* __re
 // state), results leave as 8- or 16-byte stores. Steps of few rows take one row a thread.
 template <int K, int kTokensPerThread>
 __global__ void canon_conv_vec_kernel(const float* __restrict__ h, const float* __restrict__ taps_a,
-                                      const float* __restrict__ taps_b, const float* __restrict__ state,
+                                      const float* __restrict__ taps_b, float* state,
                                       long long state_stride, const int* __restrict__ cu_seqlens,
                                       const int* __restrict__ seq_of_token, const int* __restrict__ slots,
                                       void* __restrict__ out_a, void* __restrict__ out_b, int dtype, int width,
-                                      int n_tokens) {
+                                      int n_tokens, int fuse_tail) {
   const int t0 = blockIdx.x * kTokensPerThread;
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
   if (c >= width) return;
@@ -117,6 +121,11 @@ __global__ void canon_conv_vec_kernel(const float* __restrict__ h, const float* 
     }
     emit(wa, x, out_a, t);
     if (taps_b) emit(wb, x, out_b, t);
+    if (kTokensPerThread == 1 && fuse_tail) {      // the request's only token of the step: this thread alone reads
+      float* tw = state + (size_t)slots[s] * state_stride;   // and writes these channels of its state
+#pragma unroll
+      for (int j = 1; j < K; ++j) *reinterpret_cast<float4*>(tw + (size_t)(j - 1) * width + c) = x[j];
+    }
   }
 }
 
@@ -240,20 +249,22 @@ extern "C" int hb_canon_conv(const float* h, const float* taps_a, const float* t
   int per = (width + 255) / 256;
   if (per > 32) per = 32;
   auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  int fuse = update_state == 2;     // every request brings exactly one token: the kernel moves the state itself
   const bool vec = width % 4 == 0 && state_stride % 4 == 0 && taps_n <= 4 && (width / 4 + 127) / 128 <= 65535 &&
                    aligned16(h) && aligned16(state) && aligned16(taps_a) && aligned16(taps_b) && aligned16(out_a) &&
                    aligned16(out_b);
   if (vec) {
     const int per_thread = n_tokens >= 1024 ? 8 : 1;
+    fuse = update_state == 2 && per_thread == 1;
     const dim3 grid((n_tokens + per_thread - 1) / per_thread, (width / 4 + 127) / 128);
 #define HB_CANON_VEC(K)                                                                                          \
     do {                                                                                                         \
       if (per_thread == 8)                                                                                       \
         canon_conv_vec_kernel<K, 8><<<grid, 128, 0, stream>>>(h, taps_a, taps_b, state, state_stride, cu_seqlens, \
-                                                              seq_of_token, slots, out_a, out_b, dtype, width, n_tokens); \
+                                                              seq_of_token, slots, out_a, out_b, dtype, width, n_tokens, fuse); \
       else                                                                                                       \
         canon_conv_vec_kernel<K, 1><<<grid, 128, 0, stream>>>(h, taps_a, taps_b, state, state_stride, cu_seqlens, \
-                                                              seq_of_token, slots, out_a, out_b, dtype, width, n_tokens); \
+                                                              seq_of_token, slots, out_a, out_b, dtype, width, n_tokens, fuse); \
     } while (0)
     if (taps_n == 1) HB_CANON_VEC(1);
     else if (taps_n == 2) HB_CANON_VEC(2);
@@ -262,10 +273,10 @@ extern "C" int hb_canon_conv(const float* h, const float* taps_a, const float* t
 #undef HB_CANON_VEC
   } else {
     canon_conv_kernel<<<dim3(n_tokens, per), 256, 0, stream>>>(h, taps_a, taps_b, state, state_stride, cu_seqlens,
-                                                              seq_of_token, slots, out_a, out_b, dtype, width, taps_n);
+                                                              seq_of_token, slots, out_a, out_b, dtype, width, taps_n, fuse);
   }
   HB_LAUNCH_CHECK();
-  if (update_state && taps_n > 1 && n_seqs > 0) {
+  if (update_state && !fuse && taps_n > 1 && n_seqs > 0) {
     canon_tail_kernel<<<dim3(n_seqs, per), 256, 0, stream>>>(h, state, state_stride, cu_seqlens, slots, width, taps_n);
     HB_LAUNCH_CHECK();
   }

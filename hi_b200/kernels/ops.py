@@ -403,11 +403,12 @@ def rope_copy(src: torch.Tensor, dst: torch.Tensor, positions: torch.Tensor, inv
 # --------------------------------------------------------------------------- convolved norm output, passes, two mixers
 def canon_conv(h: torch.Tensor, taps_a: torch.Tensor, taps_b: Optional[torch.Tensor], state: torch.Tensor,
                cu_seqlens: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor, out_dtype: torch.dtype,
-               update_state: bool = True):
+               update_state: bool = True, single_tokens: bool = False):
     """y[t] = h[t] + sum_j taps[:, j] * h[t - (K-1) + j] over time within each request, for ``taps_a`` and (if
     given) ``taps_b`` (float32 [W, K]); ``h`` float32 [N, W]. Rows before a portion's first token come from
     ``state[slot]`` (float32 [K-1, W] flat: the last K-1 rows of h the request has seen; zeros at its start),
-    which then takes the portion's last rows. Returns (y_a, y_b | None) in ``out_dtype``."""
+    which then takes the portion's last rows (``single_tokens``: every request brings exactly one row, and the
+    kernel moves the state itself instead of a second launch). Returns (y_a, y_b | None) in ``out_dtype``."""
     _need(h, "h", torch.float32); _need(taps_a, "taps_a", torch.float32); _need(state, "state", torch.float32)
     for t, nm in ((cu_seqlens, "cu_seqlens"), (seq_of_token, "seq_of_token"), (slots, "slots")):
         _need(t, nm, torch.int32)
@@ -423,8 +424,9 @@ def canon_conv(h: torch.Tensor, taps_a: torch.Tensor, taps_b: Optional[torch.Ten
     out_b = torch.empty_like(out_a) if taps_b is not None else None
     _check(lib().hb_canon_conv(_ptr(h), _ptr(taps_a), _ptr(taps_b), _ptr(state), state.shape[1], _ptr(cu_seqlens),
                                _ptr(seq_of_token), _ptr(slots), _ptr(out_a), _ptr(out_b), _dt(out_a), n, slots.numel(),
-                               width, k, int(update_state), _stream()), "canon_conv")
-    if update_state and k > 1:
+                               width, k, (2 if single_tokens and n < 1024 else 1) if update_state else 0, _stream()),
+           "canon_conv")
+    if update_state and k > 1 and not (single_tokens and n < 1024):
         LAUNCHES[0] += 1
     return out_a, out_b
 

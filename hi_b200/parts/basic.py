@@ -574,7 +574,7 @@ class ParallelConvBlock(Part):
         if state is None:
             raise RuntimeError(f"{self.prefix}: the block has no state rows for its convolutions")
         h_a, h_b = ops.canon_conv(h, self.taps_a, self.taps_b, state, ctx.cu_seqlens, ctx.seq_of_token, ctx.slots,
-                                  self.env.dtype)
+                                  self.env.dtype, single_tokens=ctx.max_new == 1)
         delta = layer.mixer.forward(h_a, ctx, cache_view)
         if not self.has_ff:
             return residual, Pending(dense=delta)

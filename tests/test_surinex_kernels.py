@@ -67,7 +67,8 @@ def test_canon_conv_carries_rows_between_portions(width, taps, dt, tol):
 
     state = torch.full((4, max(1, (taps - 1) * width)), 7.0, device=DEV)     # slots that are taken start from zero
     state[3].zero_(); state[1].zero_()
-    cuts = [((5, 2), (0, 0)), ((1, 1), (5, 2)), ((2, 0), (6, 3)), ((9, 14), (8, 3)), ((6, 0), (17, 17))]
+    cuts = [((5, 2), (0, 0)), ((1, 1), (5, 2)), ((2, 0), (6, 3)), ((1, 1), (8, 3)), ((0, 1), (9, 4)), ((1, 1), (9, 5)),
+            ((7, 11), (10, 6)), ((6, 0), (17, 17))]
     got_a, got_b = [[], []], [[], []]
     for ns, starts in cuts:
         live = [i for i in range(2) if ns[i] > 0]
@@ -76,7 +77,8 @@ def test_canon_conv_carries_rows_between_portions(width, taps, dt, tol):
         for i in live:
             cu.append(cu[-1] + ns[i])
         sot = [k for k, i in enumerate(live) for _ in range(ns[i])]
-        ya, yb = ops.canon_conv(h, ta.to(DEV), tb.to(DEV), state, i32(cu), i32(sot), i32([(3, 1)[i] for i in live]), dt)
+        ya, yb = ops.canon_conv(h, ta.to(DEV), tb.to(DEV), state, i32(cu), i32(sot), i32([(3, 1)[i] for i in live]), dt,
+                                single_tokens=all(ns[i] == 1 for i in live))      # then the kernel moves the state itself
         for k, i in enumerate(live):
             got_a[i].append(ya[cu[k]: cu[k + 1]])
             got_b[i].append(yb[cu[k]: cu[k + 1]])
