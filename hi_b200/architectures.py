@@ -4,11 +4,13 @@ architecture is added the same way from anywhere: a typed config reader, a build
 :func:`~hi_b200.config.registry.register_architecture` under its ``architectures`` /
 ``model_type`` names (the reference routes ``llama4`` / ``llama4_text`` to its Llama 4 model:
 crates/hi-mlx/src/config.rs:620-637, crates/hi-mlx/src/models.rs:373-375)."""
+from .config import bezasun as _bezasun
 from .config import fidatar as _fidatar
 from .config import surinex as _surinex
 from .config import vinurax as _vinurax
 from .config.llama4 import Llama4TextConfig
 from .config.registry import Architecture, register_architecture
+from .parts.bezasun import build_bezasun_spec, normalize_bezasun_tensor_name
 from .parts.fidatar import build_fidatar_spec, normalize_fidatar_tensor_name
 from .parts.llama4 import build_llama4_spec, derive_llama4_tensors, normalize_llama4_tensor_name
 from .parts.surinex import build_surinex_spec, normalize_surinex_tensor_name
@@ -33,3 +35,8 @@ register_architecture(
     ["Surinex", "surinex"],
     Architecture(name="surinex", parse_config=_surinex.SurinexConfig.from_json, build_spec=build_surinex_spec,
                  normalize_tensor_name=normalize_surinex_tensor_name, sizes_from_tensors=_surinex.sizes_from_tensors))
+
+register_architecture(
+    ["Bezasun", "bezasun"],
+    Architecture(name="bezasun", parse_config=_bezasun.BezasunConfig.from_json, build_spec=build_bezasun_spec,
+                 normalize_tensor_name=normalize_bezasun_tensor_name))

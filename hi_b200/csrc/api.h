@@ -37,15 +37,18 @@ int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, int rot_pairs
                 cudaStream_t stream);
 
 // sink != 0 (every attention entry point): the softmax's denominator has one more term of score 0,
-// p_j = e^{s_j} / (1 + sum e^{s_j}); the term has no value
+// p_j = e^{s_j} / (1 + sum e^{s_j}); the term has no value. The general kernel and the merge also take
+// sink_values (float32 [nh] or null): the term's score is the head's own number instead of 0. The general
+// kernel takes softcap (> 0: s <- softcap tanh(s / softcap) after the scale) and slopes (float32 [nh] or null:
+// slopes[h] * (query position - key position) is taken off the score after the cap).
 int hb_paged_attention(const void* q, int dtype, const void* k_pages, const void* v_pages,
                        const int* block_table, int table_stride, const int* seq_of_token, const int* positions,
                        void* out, int n_tokens, int nh, int nkv, int hd, int page_size, int chunk, int window,
-                       float scale, int sink, int split_size, int max_splits, float* part_acc, float* part_ml,
-                       cudaStream_t stream);
+                       float scale, int sink, float softcap, const float* slopes, const float* sink_values,
+                       int split_size, int max_splits, float* part_acc, float* part_ml, cudaStream_t stream);
 
 int hb_attention_merge(const float* part_acc, const float* part_ml, void* out, int dtype, int n_rows, int hd,
-                       int max_splits, int sink, cudaStream_t stream);
+                       int max_splits, int sink, int nh, const float* sink_values, cudaStream_t stream);
 int hb_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                         int table_stride, const int* seq_of_token, const int* positions, void* out, int n_tokens,
                         int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int sink,
@@ -139,10 +142,10 @@ int hb_xielu(const void* in, void* out, int dtype, const float* coef, long long 
 int hb_latent_append(const void* in, int dtype, long long in_stride, const void* w, float eps, const int* positions,
                      const int* seq_of_token, const int* block_table, int table_stride, void* pages, int page_size,
                      int rank, int row_len, int n_tokens, const float* inv_freq, int rot_pairs, int interleaved,
-                     cudaStream_t stream);
+                     float rot_mul, cudaStream_t stream);   // rot_mul: a factor on cos and sin
 int hb_rope_copy(const void* src, long long src_row, long long src_head, void* dst, long long dst_row,
                  long long dst_head, int dtype, const int* positions, const float* inv_freq, int n_tokens, int heads,
-                 int pairs, int interleaved, cudaStream_t stream);
+                 int pairs, int interleaved, float rot_mul, cudaStream_t stream);
 int hb_rmsnorm_rows(const void* in, int dtype, long long in_stride, const void* w, float eps, void* out, int n_rows,
                     int width, cudaStream_t stream);
 int hb_head_gate(const void* in, const void* gate, long long gate_stride, void* out, int dtype, int n_tokens,
@@ -208,6 +211,28 @@ int hb_sigmoid_attention(const void* q, int dtype, const void* k_pages, const vo
 int hb_sigmoid_merge(const float* part_acc, const int* positions, const float* v_inv_freq, int v_pairs,
                      int v_interleaved, void* out, int dtype, int n_tokens, int nh, int hd, int max_splits,
                      cudaStream_t stream);
+
+// hyper.cu: a residual stream of n_streams copies per token (float32 [N, S, W]). One launch per sub-layer boundary:
+// the result the sub-layer before left (delta, delta2, routed rows) goes into every copy with out_coef * mult while
+// the copies are mixed by mix [from, to] (null: the copies stay), then u = sum_s in_coef[s] x_s (null: ones) is RMS
+// normed with w into y (and y_f32). x_in: the copies do not exist yet and all equal x_in's row. row_map: only those
+// rows, nothing written back.
+int hb_hyper_step(float* streams, const float* x_in, const void* delta, int delta_dtype, const void* delta2,
+                  int delta2_dtype, const float* routed, const int* slot_of_entry, const float* routed_weight, int top_k,
+                  const float* mix, const float* out_coef, float mult, const float* in_coef, const void* w, int w_dtype,
+                  float eps, void* y, int y_dtype, float* y_f32, const int* row_map, int rows, int n_streams, int width,
+                  cudaStream_t stream);
+int hb_hyper_sum(const float* streams, float* out, int rows, int n_streams, int width, cudaStream_t stream);
+
+// mamba2.cu: what surrounds the Mamba-2 recurrence (which is hb_delta_recurrence without its correction term)
+int hb_mamba2_prep(const void* proj, int proj_dtype, long long ld, int chan_off, int dt_off, const float* taps,
+                   const float* conv_bias, const float* state, long long state_stride, long long conv_off,
+                   const float* dt_bias, const float* a_log, const int* cu_seqlens, const int* seq_of_token,
+                   const int* slots, float* x, float* v, float* k, float* q, float* decay, int n_tokens, int heads,
+                   int groups, int n_state, int vdim, int taps_n, cudaStream_t stream);
+int hb_mamba2_out(const float* o, const float* x, const void* z, int z_dtype, long long z_stride, const float* d_skip,
+                  const void* w, float eps, void* out, int dtype, int n_tokens, int heads, int vdim, int parts,
+                  cudaStream_t stream);
 
 #ifdef __cplusplus
 }

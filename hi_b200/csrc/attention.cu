@@ -20,7 +20,8 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
                                        int table_stride, const int* __restrict__ seq_of_token,
                                        const int* __restrict__ positions, T* __restrict__ out, int n_tokens,
                                        int nh, int nkv, int hd, int page_size, int chunk, int window,
-                                       float scale, int sink, int split_size, int max_splits,
+                                       float scale, int sink, float softcap, const float* __restrict__ slopes,
+                                       const float* __restrict__ sink_values, int split_size, int max_splits,
                                        float* __restrict__ part_acc, float* __restrict__ part_ml) {
   extern __shared__ float q_smem[];  // [warps][hd]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -59,6 +60,8 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
   float acc[kMaxDimsPerLane];
 #pragma unroll
   for (int i = 0; i < kMaxDimsPerLane; ++i) acc[i] = 0.f;
+  const float slope = slopes ? slopes[h] : 0.f;          // a bias of -slope * (distance to the key)
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
 
   for (int base = lo; base <= hi; base += 32) {
     const int key = base + lane;
@@ -77,6 +80,8 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
           for (int e = 0; e < 8; ++e) dot += qs[d + e] * kv[e];
         }
         s = dot;
+        if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
+        s -= slope * (float)(pos - key);
       }
     }
     const float m_new = fmaxf(m, hb::warp_max(s));
@@ -113,7 +118,8 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
     }
     return;
   }
-  if (sink && l > 0.f) l += expf(-m);      // one more term of score 0 in the denominator; it has no value
+  // one more term in the denominator, of score 0 or of the head's own learned score; it has no value
+  if (sink && l > 0.f) l += expf((sink_values ? sink_values[h] : 0.f) - m);
   const float inv = l > 0.f ? 1.f / l : 0.f;
   T* orow = out + ((size_t)t * nh + h) * hd;
 #pragma unroll
@@ -124,10 +130,12 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
 }
 
 // Combine the splits of each (token, head): o = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m},
-// in split order. With `sink` the denominator has one more term, e^{0 - m}: a key of score 0 and no value.
+// in split order. With `sink` the denominator has one more term, e^{0 - m}: a key of score 0 and no value
+// (with `sink_values` [nh] the term's score is the head's own; row th belongs to head th % nh).
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                       T* __restrict__ out, int hd, int max_splits, int sink) {
+                                       T* __restrict__ out, int hd, int max_splits, int sink, int nh,
+                                       const float* __restrict__ sink_values) {
   extern __shared__ float wgt[];   // [max_splits] weight of each split, then 33 floats of scratch
   float* scratch = wgt + max_splits;
   const size_t th = blockIdx.x;
@@ -155,7 +163,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
     l += ml[2 * s + 1] * e;
   }
   l = hb::block_sum(l, scratch);      // fixed tree order: the same inputs give the same sum
-  if (sink && l > 0.f) l += expf(-m);
+  if (sink && l > 0.f) l += expf((sink_values ? sink_values[th % (size_t)nh] : 0.f) - m);
   const float inv = l > 0.f ? 1.f / l : 0.f;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float o = 0.f;
@@ -184,7 +192,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
 extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages, const void* v_pages,
                                   const int* block_table, int table_stride, const int* seq_of_token,
                                   const int* positions, void* out, int n_tokens, int nh, int nkv, int hd,
-                                  int page_size, int chunk, int window, float scale, int sink, int split_size,
+                                  int page_size, int chunk, int window, float scale, int sink, float softcap,
+                                  const float* slopes, const float* sink_values, int split_size,
                                   int max_splits, float* part_acc, float* part_ml, cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !seq_of_token || !positions || !out) return HB_ERR_BAD_ARG;
   if (max_splits < 1 || (max_splits > 1 && (split_size <= 0 || !part_acc || !part_ml))) return HB_ERR_BAD_ARG;
@@ -202,7 +211,8 @@ extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages,
 #define HB_PAGED_ATTENTION(T, DPL)                                                                              \
   paged_attention_kernel<T, DPL><<<(int)blocks, warps_per_block * 32, smem, stream>>>(                          \
       (const T*)q, (const T*)k_pages, (const T*)v_pages, block_table, table_stride, seq_of_token, positions,    \
-      (T*)out, n_tokens, nh, nkv, hd, page_size, chunk, window, scale, sink, split_size, max_splits, part_acc, part_ml)
+      (T*)out, n_tokens, nh, nkv, hd, page_size, chunk, window, scale, sink, softcap, slopes, sink_values, split_size,   \
+      max_splits, part_acc, part_ml)
   if (dtype == HB_DTYPE_F32) {
     if (wide) HB_PAGED_ATTENTION(float, 16); else HB_PAGED_ATTENTION(float, 8);
   } else if (dtype == HB_DTYPE_BF16) {
@@ -214,10 +224,10 @@ extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages,
   HB_LAUNCH_CHECK();
   if (max_splits > 1) {
     if (dtype == HB_DTYPE_F32)
-      attention_merge_kernel<float><<<n_tokens * nh, 128, (max_splits + 33) * sizeof(float), stream>>>(part_acc, part_ml, (float*)out, hd, max_splits, sink);
+      attention_merge_kernel<float><<<n_tokens * nh, 128, (max_splits + 33) * sizeof(float), stream>>>(part_acc, part_ml, (float*)out, hd, max_splits, sink, nh, sink_values);
     else
       attention_merge_kernel<__nv_bfloat16><<<n_tokens * nh, 128, (max_splits + 33) * sizeof(float), stream>>>(
-          part_acc, part_ml, (__nv_bfloat16*)out, hd, max_splits, sink);
+          part_acc, part_ml, (__nv_bfloat16*)out, hd, max_splits, sink, nh, sink_values);
     HB_LAUNCH_CHECK();
   }
   return HB_OK;
@@ -225,14 +235,17 @@ extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages,
 
 // Merge of split partials alone (the decode kernel writes the same partial layout).
 extern "C" int hb_attention_merge(const float* part_acc, const float* part_ml, void* out, int dtype, int n_rows,
-                                  int hd, int max_splits, int sink, cudaStream_t stream) {
-  if (!part_acc || !part_ml || !out || n_rows < 0 || hd <= 0 || max_splits < 1) return HB_ERR_BAD_ARG;
+                                  int hd, int max_splits, int sink, int nh, const float* sink_values,
+                                  cudaStream_t stream) {
+  if (!part_acc || !part_ml || !out || n_rows < 0 || hd <= 0 || max_splits < 1 || (sink_values && nh <= 0))
+    return HB_ERR_BAD_ARG;
+  if (nh <= 0) nh = 1;
   if (n_rows == 0) return HB_OK;
   if (dtype == HB_DTYPE_F32)
-    attention_merge_kernel<float><<<n_rows, 128, (max_splits + 33) * sizeof(float), stream>>>(part_acc, part_ml, (float*)out, hd, max_splits, sink);
+    attention_merge_kernel<float><<<n_rows, 128, (max_splits + 33) * sizeof(float), stream>>>(part_acc, part_ml, (float*)out, hd, max_splits, sink, nh, sink_values);
   else if (dtype == HB_DTYPE_BF16)
     attention_merge_kernel<__nv_bfloat16><<<n_rows, 128, (max_splits + 33) * sizeof(float), stream>>>(
-        part_acc, part_ml, (__nv_bfloat16*)out, hd, max_splits, sink);
+        part_acc, part_ml, (__nv_bfloat16*)out, hd, max_splits, sink, nh, sink_values);
   else
     return HB_ERR_BAD_ARG;
   HB_LAUNCH_CHECK();

@@ -437,5 +437,5 @@ extern "C" int hb_attention_decode_static(const void* q, const void* k_pages, co
   int rc = hb_attention_decode(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
                                nh, nkv, hd, page_size, chunk, window, scale, 0, nullptr, split_size, max_splits, acc, ml, stream);
   if (rc != HB_OK || max_splits == 1 || n_tokens == 0) return rc;
-  return hb_attention_merge(acc, ml, out, HB_DTYPE_BF16, n_tokens * nh, hd, max_splits, 0, stream);
+  return hb_attention_merge(acc, ml, out, HB_DTYPE_BF16, n_tokens * nh, hd, max_splits, 0, nh, nullptr, stream);
 }

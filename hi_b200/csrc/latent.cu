@@ -7,7 +7,8 @@
 //                   zero-filled up to the page's row length
 //                   With a rotated key part (rot_pairs > 0): the 2 * rot_pairs inputs behind the first `rank`
 //                   are not normed; they are rotated by the token's position (pairs (i, i + rot_pairs), or
-//                   (2i, 2i + 1)) and written behind the latent, so a row is [c | rotated key part | zeros].
+//                   (2i, 2i + 1); cos and sin times rot_mul) and written behind the latent, so a row is
+//                   [c | rotated key part | zeros].
 //   rope_copy:      dst[t, h, :2 * pairs] = src[t, h, :2 * pairs] rotated by the token's position: the rotated
 //                   part of every query head, put where the attention kernel reads it
 //   rmsnorm_rows:   y = x / sqrt(mean(x^2) + eps) * w over rows that are column slices (a query latent)
@@ -22,7 +23,7 @@ __global__ void latent_append_kernel(const T* __restrict__ in, long long in_stri
                                      const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                      const int* __restrict__ block_table, int table_stride, T* __restrict__ pages,
                                      int page_size, int rank, int row_len, const float* __restrict__ inv_freq,
-                                     int rot_pairs, int interleaved) {
+                                     int rot_pairs, int interleaved, float rot_mul) {
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   const T* row = in + (size_t)t * in_stride;
@@ -48,6 +49,7 @@ __global__ void latent_append_kernel(const T* __restrict__ in, long long in_stri
       const float other = hb::to_f32(row[rank + (interleaved ? (d ^ 1) : (first ? d + rot_pairs : d - rot_pairs))]);
       float sn, cs;
       sincosf((float)pos * inv_freq[m], &sn, &cs);
+      sn *= rot_mul; cs *= rot_mul;
       y = first ? mine * cs - other * sn : mine * cs + other * sn;
     }
     dst[j] = hb::from_f32<T>(y);
@@ -59,7 +61,7 @@ template <typename T>
 __global__ void rope_copy_kernel(const T* __restrict__ src, long long src_row, long long src_head,
                                  T* __restrict__ dst, long long dst_row, long long dst_head,
                                  const int* __restrict__ positions, const float* __restrict__ inv_freq, int heads,
-                                 int pairs, int interleaved) {
+                                 int pairs, int interleaved, float rot_mul) {
   const size_t t = blockIdx.x;
   const int pos = positions[t];
   const int dims = 2 * pairs;
@@ -72,6 +74,7 @@ __global__ void rope_copy_kernel(const T* __restrict__ src, long long src_row, l
     const float other = hb::to_f32(s[interleaved ? (d ^ 1) : (first ? d + pairs : d - pairs)]);
     float sn, cs;
     sincosf((float)pos * inv_freq[m], &sn, &cs);
+    sn *= rot_mul; cs *= rot_mul;
     dst[t * dst_row + (size_t)h * dst_head + d] = hb::from_f32<T>(first ? mine * cs - other * sn : mine * cs + other * sn);
   }
 }
@@ -110,7 +113,8 @@ __global__ void head_gate_kernel(const T* __restrict__ in, const T* __restrict__
 extern "C" int hb_latent_append(const void* in, int dtype, long long in_stride, const void* w, float eps,
                                 const int* positions, const int* seq_of_token, const int* block_table,
                                 int table_stride, void* pages, int page_size, int rank, int row_len, int n_tokens,
-                                const float* inv_freq, int rot_pairs, int interleaved, cudaStream_t stream) {
+                                const float* inv_freq, int rot_pairs, int interleaved, float rot_mul,
+                                cudaStream_t stream) {
   if (!in || !w || !positions || !seq_of_token || !block_table || !pages) return HB_ERR_BAD_ARG;
   if (!inv_freq) rot_pairs = 0;
   if (rank <= 0 || rot_pairs < 0 || row_len < rank + 2 * rot_pairs || page_size <= 0 || table_stride <= 0 ||
@@ -121,11 +125,11 @@ extern "C" int hb_latent_append(const void* in, int dtype, long long in_stride, 
   if (dtype == HB_DTYPE_F32)
     latent_append_kernel<float><<<n_tokens, threads, 0, stream>>>(
         (const float*)in, in_stride, (const float*)w, eps, positions, seq_of_token, block_table, table_stride,
-        (float*)pages, page_size, rank, row_len, inv_freq, rot_pairs, interleaved);
+        (float*)pages, page_size, rank, row_len, inv_freq, rot_pairs, interleaved, rot_mul);
   else if (dtype == HB_DTYPE_BF16)
     latent_append_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
         (const __nv_bfloat16*)in, in_stride, (const __nv_bfloat16*)w, eps, positions, seq_of_token, block_table,
-        table_stride, (__nv_bfloat16*)pages, page_size, rank, row_len, inv_freq, rot_pairs, interleaved);
+        table_stride, (__nv_bfloat16*)pages, page_size, rank, row_len, inv_freq, rot_pairs, interleaved, rot_mul);
   else
     return HB_ERR_BAD_ARG;
   HB_LAUNCH_CHECK();
@@ -134,18 +138,18 @@ extern "C" int hb_latent_append(const void* in, int dtype, long long in_stride, 
 
 extern "C" int hb_rope_copy(const void* src, long long src_row, long long src_head, void* dst, long long dst_row,
                             long long dst_head, int dtype, const int* positions, const float* inv_freq, int n_tokens,
-                            int heads, int pairs, int interleaved, cudaStream_t stream) {
+                            int heads, int pairs, int interleaved, float rot_mul, cudaStream_t stream) {
   if (!src || !dst || !positions || !inv_freq || n_tokens < 0 || heads <= 0 || pairs <= 0) return HB_ERR_BAD_ARG;
   if (n_tokens == 0) return HB_OK;
   const int work = heads * 2 * pairs;
   const int threads = work >= 256 ? 256 : (work + 31) / 32 * 32;
   if (dtype == HB_DTYPE_F32)
     rope_copy_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)src, src_row, src_head, (float*)dst, dst_row,
-                                                              dst_head, positions, inv_freq, heads, pairs, interleaved);
+                                                              dst_head, positions, inv_freq, heads, pairs, interleaved, rot_mul);
   else if (dtype == HB_DTYPE_BF16)
     rope_copy_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
         (const __nv_bfloat16*)src, src_row, src_head, (__nv_bfloat16*)dst, dst_row, dst_head, positions, inv_freq,
-        heads, pairs, interleaved);
+        heads, pairs, interleaved, rot_mul);
   else
     return HB_ERR_BAD_ARG;
   HB_LAUNCH_CHECK();

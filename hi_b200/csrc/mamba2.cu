@@ -1,0 +1,164 @@
+// The Mamba-2 mixer around its recurrence. With heads of vdim value channels, G groups of N state channels and
+// one projection row per token laid out as [z: heads*vdim | x: heads*vdim | B: G*N | C: G*N | dt: heads]:
+//
+//   mamba2_prep   per token: causal convolution over time (taps [C, K] float32, last column the token's own,
+//                 plus a bias per channel) and silu of the x | B | C channels (rows before the portion's first
+//                 token come from the request's state); dt = softplus(dt + dt_bias), no clamp;
+//                 decay = exp(-exp(A_log[h]) * dt), written out per state channel of the head;
+//                 x (float32, for the skip), v = dt * x, k = B, q = C.
+//                 The recurrence itself is the delta rule's kernel without its correction term
+//                 (S <- decay * S + k v^T, o = S^T q; S [N, vdim] per head, a head reads its group's B and C),
+//                 and the state's convolution rows are moved by hb_delta_conv_update.
+//   mamba2_out    y = (o + D[h] * x) * silu(z); RMS norm of y in `parts` equal runs of channels, each by its own
+//                 root mean square; times a weight per channel; rounded to the engine's dtype.
+//
+// Everything between the projection and the normed output is float32.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float ldf(const void* p, int dtype, size_t i) {
+  return dtype == HB_DTYPE_F32 ? reinterpret_cast<const float*>(p)[i]
+                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ float silu1(float v) { return v / (1.f + expf(-v)); }
+
+struct MambaPrepArgs {
+  const void* proj;      // [N, ld]
+  int proj_dtype;
+  long long ld;
+  int chan_off, dt_off;  // first column of the x | B | C channels, of dt
+  const float* taps;     // [C, K]
+  const float* conv_bias;  // [C]
+  const float* state;    // [slots, state_stride]; the convolution's last K-1 inputs [K-1, C] at conv_off
+  long long state_stride, conv_off;
+  const float* dt_bias;  // [heads]
+  const float* a_log;    // [heads]
+  const int* cu_seqlens;
+  const int* seq_of_token;
+  const int* slots;
+  float* x;              // [N, heads * vdim]
+  float* v;              // [N, heads * vdim]   dt * x
+  float* k;              // [N, G * N]          B
+  float* q;              // [N, G * N]          C
+  float* decay;          // [N, heads * N]
+  int heads, groups, n_state, vdim, K;
+};
+
+// grid (tokens, groups of units), a warp per unit: a unit is one head's x channels (with its dt and decay) or one
+// group's B or C channels.
+__global__ void mamba2_prep_kernel(const MambaPrepArgs a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int t = blockIdx.x;
+  const int s = a.seq_of_token[t];
+  const int start = a.cu_seqlens[s];
+  const int local = t - start;
+  const int inner = a.heads * a.vdim, gn = a.groups * a.n_state, C = inner + 2 * gn, K = a.K;
+  const float* conv = a.state + (size_t)a.slots[s] * a.state_stride + a.conv_off;   // [K-1, C]
+  const int units = a.heads + 2 * a.groups;
+  for (int u = blockIdx.y * warps + warp; u < units; u += gridDim.y * warps) {
+    const bool is_x = u < a.heads;
+    const int len = is_x ? a.vdim : a.n_state;
+    const int c0 = is_x ? u * a.vdim : inner + (u - a.heads) * a.n_state;
+    float dt = 0.f;
+    if (is_x) {
+      const float z = ldf(a.proj, a.proj_dtype, (size_t)t * a.ld + a.dt_off + u) + a.dt_bias[u];
+      dt = z > 20.f ? z : log1pf(expf(z));
+      const float g = expf(-expf(a.a_log[u]) * dt);
+      for (int i = lane; i < a.n_state; i += 32) a.decay[((size_t)t * a.heads + u) * a.n_state + i] = g;
+    }
+    for (int i = lane; i < len; i += 32) {
+      const int c = c0 + i;
+      float acc = a.conv_bias ? a.conv_bias[c] : 0.f;
+      for (int j = 0; j < K; ++j) {
+        const int rel = local - (K - 1) + j;
+        const float xin = rel >= 0 ? ldf(a.proj, a.proj_dtype, (size_t)(start + rel) * a.ld + a.chan_off + c)
+                                   : conv[(size_t)(K - 1 + rel) * C + c];
+        acc += a.taps[(size_t)c * K + j] * xin;
+      }
+      const float y = silu1(acc);
+      if (is_x) {
+        a.x[(size_t)t * inner + c] = y;
+        a.v[(size_t)t * inner + c] = dt * y;
+      } else if (c < inner + gn) {
+        a.k[(size_t)t * gn + (c - inner)] = y;
+      } else {
+        a.q[(size_t)t * gn + (c - inner - gn)] = y;
+      }
+    }
+  }
+}
+
+// grid (tokens, parts); a block norms one run of inner / parts channels.
+template <typename T>
+__global__ void mamba2_out_kernel(const float* __restrict__ o, const float* __restrict__ x, const void* __restrict__ z,
+                                  int z_dtype, long long z_stride, const float* __restrict__ d_skip,
+                                  const T* __restrict__ w, float eps, T* __restrict__ out, int inner, int vdim, int run) {
+  __shared__ float scratch[33];
+  const size_t t = blockIdx.x;
+  const int c0 = blockIdx.y * run;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < run; i += blockDim.x) {
+    const int c = c0 + i;
+    const float y = (o[t * inner + c] + d_skip[c / vdim] * x[t * inner + c]) * silu1(ldf(z, z_dtype, t * z_stride + c));
+    ss += y * y;
+  }
+  const float inv = rsqrtf(hb::block_sum(ss, scratch) / (float)run + eps);
+  for (int i = threadIdx.x; i < run; i += blockDim.x) {
+    const int c = c0 + i;
+    const float y = (o[t * inner + c] + d_skip[c / vdim] * x[t * inner + c]) * silu1(ldf(z, z_dtype, t * z_stride + c));
+    out[t * inner + c] = hb::from_f32<T>(y * inv * hb::to_f32(w[c]));
+  }
+}
+
+}  // namespace
+
+extern "C" int hb_mamba2_prep(const void* proj, int proj_dtype, long long ld, int chan_off, int dt_off, const float* taps,
+                              const float* conv_bias, const float* state, long long state_stride, long long conv_off,
+                              const float* dt_bias, const float* a_log, const int* cu_seqlens, const int* seq_of_token,
+                              const int* slots, float* x, float* v, float* k, float* q, float* decay, int n_tokens,
+                              int heads, int groups, int n_state, int vdim, int taps_n, cudaStream_t stream) {
+  if (!proj || !taps || !state || !dt_bias || !a_log || !cu_seqlens || !seq_of_token || !slots || !x || !v || !k || !q ||
+      !decay)
+    return HB_ERR_BAD_ARG;
+  if (n_tokens < 0 || heads <= 0 || groups <= 0 || heads % groups || n_state <= 0 || vdim <= 0 || taps_n < 1)
+    return HB_ERR_BAD_ARG;
+  if (n_tokens == 0) return HB_OK;
+  MambaPrepArgs a;
+  a.proj = proj; a.proj_dtype = proj_dtype; a.ld = ld; a.chan_off = chan_off; a.dt_off = dt_off; a.taps = taps;
+  a.conv_bias = conv_bias; a.state = state; a.state_stride = state_stride; a.conv_off = conv_off; a.dt_bias = dt_bias;
+  a.a_log = a_log; a.cu_seqlens = cu_seqlens; a.seq_of_token = seq_of_token; a.slots = slots; a.x = x; a.v = v; a.k = k;
+  a.q = q; a.decay = decay; a.heads = heads; a.groups = groups; a.n_state = n_state; a.vdim = vdim; a.K = taps_n;
+  const int units = heads + 2 * groups;
+  const int warps = units < 4 ? units : 4;
+  int gy = (units + warps - 1) / warps;
+  if (gy > 64) gy = 64;
+  mamba2_prep_kernel<<<dim3(n_tokens, gy), warps * 32, 0, stream>>>(a);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+extern "C" int hb_mamba2_out(const float* o, const float* x, const void* z, int z_dtype, long long z_stride,
+                             const float* d_skip, const void* w, float eps, void* out, int dtype, int n_tokens, int heads,
+                             int vdim, int parts, cudaStream_t stream) {
+  if (!o || !x || !z || !d_skip || !w || !out || n_tokens < 0 || heads <= 0 || vdim <= 0 || parts <= 0)
+    return HB_ERR_BAD_ARG;
+  const int inner = heads * vdim;
+  if (inner % parts || z_stride < inner || parts > 65535) return HB_ERR_BAD_ARG;
+  if (n_tokens == 0) return HB_OK;
+  const int run = inner / parts;
+  const int threads = run >= 1024 ? 256 : (run >= 128 ? 128 : (run + 31) / 32 * 32);
+  const dim3 grid(n_tokens, parts);
+  if (dtype == HB_DTYPE_F32)
+    mamba2_out_kernel<float><<<grid, threads, 0, stream>>>(o, x, z, z_dtype, z_stride, d_skip, (const float*)w, eps,
+                                                           (float*)out, inner, vdim, run);
+  else if (dtype == HB_DTYPE_BF16)
+    mamba2_out_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(o, x, z, z_dtype, z_stride, d_skip,
+                                                                   (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)out,
+                                                                   inner, vdim, run);
+  else
+    return HB_ERR_BAD_ARG;
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}

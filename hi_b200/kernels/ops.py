@@ -26,8 +26,8 @@ _SIGNATURES = {
     "hb_convert": [P, I, P, I, c_longlong, P],
     "hb_moe_combine": [P, P, P, P, I, P, I, I, I, P],
     "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, I, I, F, P, I, I, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
-    "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P],
-    "hb_attention_merge": [P, P, P, I, I, I, I, I, P],
+    "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, F, P, P, I, I, P, P, P],
+    "hb_attention_merge": [P, P, P, I, I, I, I, I, I, P, P],
     "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, I, I, P, P, P],
     "hb_attention_decode_tma": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
     "hb_attention_decode_fused": [P, P, I, I, I, F, I, F, F, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P, P, I, F, I, P],
@@ -51,9 +51,9 @@ _SIGNATURES = {
     "hb_random_normal": [P, I, c_longlong, c_longlong, c_uint64, F, P],
     "hb_gated_depth_dyt": [P, P, I, P, I, P, I, P, I, P, c_longlong, I, P, P, P, P, P, P, P, P, P, P, I, I, P, I, I, P],
     "hb_xielu": [P, P, I, P, c_longlong, P],
-    "hb_latent_append": [P, I, c_longlong, P, F, P, P, P, I, P, I, I, I, I, P, I, I, P],
+    "hb_latent_append": [P, I, c_longlong, P, F, P, P, P, I, P, I, I, I, I, P, I, I, F, P],
     "hb_rmsnorm_rows": [P, I, c_longlong, P, F, P, I, I, P],
-    "hb_rope_copy": [P, c_longlong, c_longlong, P, c_longlong, c_longlong, I, P, P, I, I, I, I, P],
+    "hb_rope_copy": [P, c_longlong, c_longlong, P, c_longlong, c_longlong, I, P, P, I, I, I, I, F, P],
     "hb_canon_conv": [P, P, P, P, c_longlong, P, P, P, P, P, I, I, I, I, I, I, P],
     "hb_stream_add": [P, P, I, P, I, P, P, c_longlong, I, P],
     "hb_rmsnorm_mean2": [P, P, I, P, P, I, F, P, I, I, I, P],
@@ -65,6 +65,11 @@ _SIGNATURES = {
     "hb_delta_conv_update": [P, I, c_longlong, I, P, c_longlong, c_longlong, P, P, I, I, I, P],
     "hb_delta_recurrence": [P, P, P, P, P, P, c_longlong, P, P, P, I, I, I, I, I, I, I, I, P],
     "hb_delta_out_norm": [P, P, I, P, F, P, I, c_longlong, I, I, c_longlong, I, P],
+    "hb_hyper_step": [P, P, P, I, P, I, P, P, P, I, P, P, F, P, P, I, F, P, I, P, P, I, I, I, P],
+    "hb_hyper_sum": [P, P, I, I, I, P],
+    "hb_mamba2_prep": [P, I, c_longlong, I, I, P, P, P, c_longlong, c_longlong, P, P, P, P, P, P, P, P, P, P, I, I, I, I,
+                       I, I, P],
+    "hb_mamba2_out": [P, P, P, I, c_longlong, P, P, F, P, I, I, I, I, I, P],
     "hb_mlstm_gates": [P, P, P, F, P, c_longlong, c_longlong, P, P, P, P, P, I, I, P],
     "hb_mlstm_recurrence": [P, I, c_longlong, I, I, I, F, P, P, P, c_longlong, P, P, P, P, I, I, I, I, I, P],
     "hb_mlstm_out_norm": [P, P, P, P, I, c_longlong, I, P, I, F, P, I, c_longlong, I, I, P],
@@ -345,14 +350,14 @@ def _row_strided(t: torch.Tensor, name: str) -> int:
 
 def latent_append(x: torch.Tensor, weight: torch.Tensor, eps: float, positions: torch.Tensor,
                   seq_of_token: torch.Tensor, block_table: torch.Tensor, pages: torch.Tensor,
-                  inv_freq: Optional[torch.Tensor] = None, interleaved: bool = False) -> None:
+                  inv_freq: Optional[torch.Tensor] = None, interleaved: bool = False, rot_mul: float = 1.0) -> None:
     """pages[page of token, 0, place, :rank] = x / sqrt(mean(x^2) + eps) * weight for every token's row of
     ``x`` [N, rank] (rows may be a column slice of a wider matrix); ``pages`` [P, 1, page_size, row_len >= rank],
     the rest of a row is zero-filled. Statistics in float32.
 
     With ``inv_freq`` (float32 [pairs]) ``x`` is [N, rank + 2 * pairs]: the columns behind the latent are a key
     part that is not normed but rotated by the token's position (pairs (i, i + pairs), or (2i, 2i + 1) with
-    ``interleaved``) and written behind the latent in the page row."""
+    ``interleaved``; cos and sin times ``rot_mul``) and written behind the latent in the page row."""
     stride = _row_strided(x, "x")
     _need(weight, "weight", x.dtype); _need(pages, "pages", x.dtype)
     for t, nm in ((positions, "positions"), (seq_of_token, "seq_of_token"), (block_table, "block_table")):
@@ -366,7 +371,8 @@ def latent_append(x: torch.Tensor, weight: torch.Tensor, eps: float, positions: 
         raise KernelError(f"pages {tuple(pages.shape)} / weight do not take latents of {rank} (+ {2 * pairs} rotated)")
     _check(lib().hb_latent_append(_ptr(x), _dt(x), stride, _ptr(weight), float(eps), _ptr(positions), _ptr(seq_of_token),
                                   _ptr(block_table), block_table.shape[1], _ptr(pages), pages.shape[2], rank,
-                                  pages.shape[3], n, _ptr(inv_freq), pairs, int(interleaved), _stream()), "latent_append")
+                                  pages.shape[3], n, _ptr(inv_freq), pairs, int(interleaved), float(rot_mul), _stream()),
+           "latent_append")
 
 
 def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -384,9 +390,9 @@ def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Ten
 
 
 def rope_copy(src: torch.Tensor, dst: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
-              interleaved: bool = False) -> None:
+              interleaved: bool = False, rot_mul: float = 1.0) -> None:
     """dst[t, h, :2p] = src[t, h, :2p] rotated by positions[t] (p = len(inv_freq) pairs; (i, i + p), or
-    (2i, 2i + 1) with ``interleaved``). ``src`` and ``dst`` are [N, heads, >= 2p] views whose last axis is
+    (2i, 2i + 1) with ``interleaved``; cos and sin times ``rot_mul``). ``src`` and ``dst`` are [N, heads, >= 2p] views whose last axis is
     contiguous (slices of wider tensors), of one dtype; they may be the same memory."""
     _need(positions, "positions", torch.int32); _need(inv_freq, "inv_freq", torch.float32)
     pairs = inv_freq.numel()
@@ -397,7 +403,7 @@ def rope_copy(src: torch.Tensor, dst: torch.Tensor, positions: torch.Tensor, inv
         raise KernelError("src and dst need one dtype and the same tokens and heads")
     _check(lib().hb_rope_copy(_ptr(src), src.stride(0), src.stride(1), _ptr(dst), dst.stride(0), dst.stride(1), _dt(src),
                               _ptr(positions), _ptr(inv_freq), src.shape[0], src.shape[1], pairs, int(interleaved),
-                              _stream()), "rope_copy")
+                              float(rot_mul), _stream()), "rope_copy")
 
 
 # --------------------------------------------------------------------------- convolved norm output, passes, two mixers
@@ -597,6 +603,144 @@ def gla_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, z: torch.Te
     return q, k, v, decay
 
 
+# --------------------------------------------------------------------------- a residual stream of several copies
+def hyper_step(streams: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+               x_in: Optional[torch.Tensor] = None, delta: Optional[torch.Tensor] = None,
+               delta2: Optional[torch.Tensor] = None, routed: Optional[torch.Tensor] = None,
+               slot_of_entry: Optional[torch.Tensor] = None, top_k: int = 0,
+               routed_weight: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+               out_coef: Optional[torch.Tensor] = None, mult: float = 1.0, in_coef: Optional[torch.Tensor] = None,
+               row_map: Optional[torch.Tensor] = None, also_f32: bool = False):
+    """One sub-layer boundary of a residual stream kept as S copies per token (``streams`` float32 [N, S, W], in place).
+
+    The result the sub-layer before left (``delta`` + ``delta2`` + the routed rows, as in :func:`add_rmsnorm`) enters
+    every copy while the copies are mixed: x_t <- sum_s mix[s, t] x_s + mult * out_coef[t] * y (``mix`` None: the
+    copies stay). Then u = sum_s in_coef[s] x_s (``in_coef`` None: the plain sum) and the result is
+    u * rsqrt(mean(u^2) + eps) * weight in ``out_dtype`` (with ``also_f32`` a pair: rounded, unrounded).
+    ``x_in`` (float32 [N, W]): the copies do not exist yet, every one of them is ``x_in``'s row, and they are written.
+    ``row_map`` (int32 [R]): only those rows, output [R, W], nothing written back."""
+    _need(streams, "streams", torch.float32)
+    if streams.dim() != 3:
+        raise KernelError("streams must be [tokens, copies, width]")
+    n, s_n, width = streams.shape
+    for t, nm in ((delta, "delta"), (delta2, "delta2")):
+        if t is not None:
+            _need(t, nm)
+            if tuple(t.shape) != (n, width):
+                raise KernelError(f"{nm} shape {tuple(t.shape)} does not match {n} tokens of width {width}")
+    if x_in is not None:
+        _need(x_in, "x_in", torch.float32)
+        if tuple(x_in.shape) != (n, width):
+            raise KernelError("x_in does not match the streams")
+    if mix is not None:
+        _need(mix, "mix", torch.float32); _need(out_coef, "out_coef", torch.float32)
+        if tuple(mix.shape) != (s_n, s_n) or out_coef.numel() != s_n:
+            raise KernelError("mix / out_coef do not match the number of copies")
+    elif delta is not None or delta2 is not None or routed is not None:
+        raise KernelError("a sub-layer result needs the coefficients it enters the copies with")
+    if in_coef is not None:
+        _need(in_coef, "in_coef", torch.float32)
+        if in_coef.numel() != s_n:
+            raise KernelError("in_coef does not match the number of copies")
+    if weight is not None:
+        _need(weight, "weight")
+        if weight.numel() != width:
+            raise KernelError(f"norm weight has {weight.numel()} elements for width {width}")
+    if routed is not None:
+        _need(routed, "routed", torch.float32); _need(slot_of_entry, "slot_of_entry", torch.int32)
+        if routed.shape[1] != width or top_k < 1 or slot_of_entry.numel() != n * top_k:
+            raise KernelError("routed rows do not match the streams")
+        if routed_weight is not None:
+            _need(routed_weight, "routed_weight", torch.float32)
+            if routed_weight.numel() != slot_of_entry.numel():
+                raise KernelError("routed_weight needs one factor per routing entry")
+    rows = n
+    if row_map is not None:
+        _need(row_map, "row_map", torch.int32)
+        rows = row_map.numel()
+    y = torch.empty((rows, width), dtype=out_dtype, device=streams.device)
+    y32 = torch.empty((rows, width), dtype=torch.float32, device=streams.device) \
+        if also_f32 and out_dtype != torch.float32 else None
+    _check(lib().hb_hyper_step(_ptr(streams), _ptr(x_in), _ptr(delta), _dt(delta) if delta is not None else 0,
+                               _ptr(delta2), _dt(delta2) if delta2 is not None else 0, _ptr(routed),
+                               _ptr(slot_of_entry) if routed is not None else None,
+                               _ptr(routed_weight) if routed is not None else None, int(top_k), _ptr(mix),
+                               _ptr(out_coef), float(mult), _ptr(in_coef), _ptr(weight),
+                               _dt(weight) if weight is not None else 0, float(eps), _ptr(y), _dt(y), _ptr(y32),
+                               _ptr(row_map), rows, s_n, width, _stream()), "hyper_step")
+    if also_f32:
+        return y, (y if y32 is None else y32)
+    return y
+
+
+def hyper_sum(streams: torch.Tensor) -> torch.Tensor:
+    """The sum of the copies of a residual stream: float32 [N, S, W] -> [N, W]."""
+    _need(streams, "streams", torch.float32)
+    n, s_n, width = streams.shape
+    out = torch.empty((n, width), dtype=torch.float32, device=streams.device)
+    _check(lib().hb_hyper_sum(_ptr(streams), _ptr(out), n, s_n, width, _stream()), "hyper_sum")
+    return out
+
+
+# --------------------------------------------------------------------------- Mamba-2 around its recurrence
+def mamba2_prep(proj: torch.Tensor, chan_off: int, dt_off: int, taps: torch.Tensor, conv_bias: Optional[torch.Tensor],
+                state: torch.Tensor, conv_off: int, dt_bias: torch.Tensor, a_log: torch.Tensor, cu_seqlens: torch.Tensor,
+                seq_of_token: torch.Tensor, slots: torch.Tensor, heads: int, groups: int, n_state: int, vdim: int):
+    """Per token, from a projection row laid out [... x | B | C ... dt ...] (``chan_off``: first column of the
+    C = heads*vdim + 2*groups*n_state convolved channels; ``dt_off``: of the heads' step sizes): causal convolution
+    over time (``taps`` float32 [C, K], last column the token's own; ``conv_bias`` [C]) and silu, rows before a
+    portion's first token from ``state[slot, conv_off:]`` ([K-1, C] float32); dt = softplus(dt + dt_bias);
+    decay = exp(-exp(a_log[h]) * dt) written out per state channel. Returns float32
+    (x [N, heads*vdim], v = dt * x, k = B [N, groups*n_state], q = C, decay [N, heads*n_state])."""
+    _need(proj, "proj"); _need(taps, "taps", torch.float32); _need(state, "state", torch.float32)
+    _need(dt_bias, "dt_bias", torch.float32); _need(a_log, "a_log", torch.float32)
+    for t, nm in ((cu_seqlens, "cu_seqlens"), (seq_of_token, "seq_of_token"), (slots, "slots")):
+        _need(t, nm, torch.int32)
+    n, ld = proj.shape
+    inner, gn = heads * vdim, groups * n_state
+    c = inner + 2 * gn
+    k_taps = taps.shape[1]
+    if tuple(taps.shape) != (c, k_taps) or chan_off + c > ld or dt_off + heads > ld:
+        raise KernelError("taps / column offsets do not fit the projection")
+    if conv_bias is not None:
+        _need(conv_bias, "conv_bias", torch.float32)
+        if conv_bias.numel() != c:
+            raise KernelError("one convolution bias per channel")
+    if dt_bias.numel() != heads or a_log.numel() != heads or heads % groups:
+        raise KernelError("dt_bias / a_log / groups do not match the heads")
+    if state.dim() != 2 or conv_off + (k_taps - 1) * c > state.shape[1]:
+        raise KernelError("the state does not hold the convolution's inputs")
+    dev, f32 = proj.device, torch.float32
+    x = torch.empty((n, inner), dtype=f32, device=dev)
+    v = torch.empty((n, inner), dtype=f32, device=dev)
+    k = torch.empty((n, gn), dtype=f32, device=dev)
+    q = torch.empty((n, gn), dtype=f32, device=dev)
+    decay = torch.empty((n, heads * n_state), dtype=f32, device=dev)
+    _check(lib().hb_mamba2_prep(_ptr(proj), _dt(proj), ld, int(chan_off), int(dt_off), _ptr(taps), _ptr(conv_bias),
+                                _ptr(state), state.shape[1], int(conv_off), _ptr(dt_bias), _ptr(a_log), _ptr(cu_seqlens),
+                                _ptr(seq_of_token), _ptr(slots), _ptr(x), _ptr(v), _ptr(k), _ptr(q), _ptr(decay), n, heads,
+                                groups, n_state, vdim, k_taps, _stream()), "mamba2_prep")
+    return x, v, k, q, decay
+
+
+def mamba2_out(o: torch.Tensor, x: torch.Tensor, z: torch.Tensor, d_skip: torch.Tensor, weight: torch.Tensor, eps: float,
+               heads: int, vdim: int, parts: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """y = (o + d_skip[head] * x) * silu(z), RMS-normed in ``parts`` equal runs of channels (each by its own root
+    mean square), times ``weight`` [heads*vdim], in ``out_dtype``. ``o``, ``x`` float32 [N, heads*vdim]; ``z`` may be
+    a column slice of a wider matrix."""
+    _need(o, "o", torch.float32); _need(x, "x", torch.float32); _need(d_skip, "d_skip", torch.float32)
+    _need(weight, "weight", out_dtype)
+    z_stride = _row_strided(z, "z")
+    inner = heads * vdim
+    if o.shape != x.shape or o.shape[1] != inner or z.shape != o.shape or d_skip.numel() != heads or \
+            weight.numel() != inner or inner % parts:
+        raise KernelError("o / x / z / d_skip / weight do not match the heads, or the parts do not divide the channels")
+    out = torch.empty(o.shape, dtype=out_dtype, device=o.device)
+    _check(lib().hb_mamba2_out(_ptr(o), _ptr(x), _ptr(z), _dt(z), z_stride, _ptr(d_skip), _ptr(weight), float(eps),
+                               _ptr(out), _dt(out), o.shape[0], heads, vdim, int(parts), _stream()), "mamba2_out")
+    return out
+
+
 # --------------------------------------------------------------------------- mLSTM matrix memory
 def mlstm_state_floats(heads: int, dim: int, vdim: int) -> int:
     """Floats of a request's state row: S column by column with n as one more column, then m per head."""
@@ -777,10 +921,14 @@ DECODE_RESIDENT_BLOCKS = 148 * 3   # blocks of the decode kernel resident at a t
 
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                     seq_of_token: torch.Tensor, positions: torch.Tensor, chunk: int, window: int,
-                    scale: float, max_context: int = 0, sink: bool = False) -> torch.Tensor:
+                    scale: float, max_context: int = 0, sink: bool = False, softcap: float = 0.0,
+                    slopes: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None) -> torch.Tensor:
     """softmax(q k^T * scale) v over the keys each token may read; q [N, nh, hd] -> [N, nh, hd].
     ``sink`` (here and in the other attention kernels): the softmax's denominator has one more term of
-    score 0, p_j = e^{s_j} / (1 + sum_j e^{s_j}); the term has no value.
+    score 0, p_j = e^{s_j} / (1 + sum_j e^{s_j}); the term has no value. ``sink_values`` (float32 [nh]): the
+    term's score is the head's own number instead of 0. ``softcap`` > 0: the scaled score becomes
+    softcap * tanh(score / softcap). ``slopes`` (float32 [nh]): slopes[h] * (query position - key position)
+    is taken off the score (after the cap).
 
     ``max_context`` (an upper bound of position + 1 over the tokens) lets long ranges be cut into
     splits of ``ATTENTION_SPLIT`` keys that run in parallel and are merged; a token's splits depend
@@ -796,6 +944,11 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         raise KernelError(f"{nh} query heads are not a multiple of {nkv} kv heads")
     if hd % 16 != 0 or hd > 512:
         raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 512)")
+    for t, nm in ((slopes, "slopes"), (sink_values, "sink_values")):
+        if t is not None:
+            _need(t, nm, torch.float32)
+            if t.numel() != nh:
+                raise KernelError(f"{nm} needs one number per query head")
     out = torch.empty_like(q)
     longest = max_context
     if chunk > 0:
@@ -809,8 +962,9 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         part_ml = torch.empty((n, nh, splits, 2), dtype=torch.float32, device=q.device)
     _check(lib().hb_paged_attention(_ptr(q), _dt(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                                     block_table.shape[1], _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv,
-                                    hd, page_size, int(chunk), int(window), float(scale), int(sink), ATTENTION_SPLIT,
-                                    splits, _ptr(part_acc), _ptr(part_ml), _stream()),
+                                    hd, page_size, int(chunk), int(window), float(scale),
+                                    int(sink or sink_values is not None), float(softcap), _ptr(slopes),
+                                    _ptr(sink_values), ATTENTION_SPLIT, splits, _ptr(part_acc), _ptr(part_ml), _stream()),
            "paged_attention")
     return out
 
@@ -1026,7 +1180,7 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         _check(code, "attention_decode_tma")
     if splits > 1:
         _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, splits,
-                                        int(sink), _stream()), "attention_merge")
+                                        int(sink), nh, None, _stream()), "attention_merge")
     return out
 
 
@@ -1103,7 +1257,7 @@ def decode_attention_fused(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positi
     _check(code, "attention_decode_fused")
     if splits > 1 and not merge_inside:
         _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, splits,
-                                        int(sink), _stream()), "attention_merge")
+                                        int(sink), nh, None, _stream()), "attention_merge")
     return out
 
 
@@ -1187,7 +1341,7 @@ def prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
     TC_USED[0] = True
     if key_splits > 1:
         _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, key_splits,
-                                        int(sink), _stream()), "attention_merge")
+                                        int(sink), nh, None, _stream()), "attention_merge")
     return out
 
 

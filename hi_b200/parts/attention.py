@@ -30,14 +30,19 @@ def _key_splits(ctx, nh: int, chunk: int, sliding: int, single: bool, device) ->
 
 
 def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, hd: int, chunk: int, sliding: int,
-                      scale: float, sink: bool = False):
+                      scale: float, sink: bool = False, softcap: float = 0.0, slopes=None, sink_values=None):
     """softmax(q k^T scale + mask) v for the step's tokens over the paged keys and values that are in
     the cache already, by the kernel that fits the step: single decoded tokens, portions of prompts
     (with single tokens of other requests beside them), or the general kernel for what those refuse
     (float32, other head sizes). ``q`` [N, nh, hd] -> [N, nh, hd]. Every mixer whose scores are dot
     products over paged rows comes through here; ``k_pages`` and ``v_pages`` may be the same pool.
-    ``sink``: the softmax's denominator has one more term of score 0 (it has no value)."""
+    ``sink``: the softmax's denominator has one more term of score 0 (it has no value); ``sink_values``
+    (float32 [nh]): of the head's own score instead. ``softcap`` > 0: scores become softcap tanh(score / softcap);
+    ``slopes`` (float32 [nh]): slopes[head] * (distance to the key) is taken off after the cap."""
     positions = ctx.positions
+    if softcap or slopes is not None or sink_values is not None:
+        return ops.paged_attention(q, k_pages, v_pages, block_table, ctx.seq_of_token, positions, chunk, sliding, scale,
+                                   ctx.max_context, sink=sink, softcap=softcap, slopes=slopes, sink_values=sink_values)
     # the decode kernel packs the query heads of one kv head into a 16-row tile; more heads on ONE shared kv
     # head go through it sixteen at a time
     per_call = nh if nkv > 1 or nh <= 16 else 16
@@ -130,7 +135,12 @@ class AttentionMixer(Part):
                        rounded up to 16): the projections get zero rows, the output projection zero columns
       ``qk_norm_weighted``  the norm of q and k is an RMS norm BEFORE the rotation with a weight per dim,
                        ``<prefix>.q.norm`` / ``<prefix>.k.norm`` [head_dim], shared by the heads
-      ``sink``         the softmax's denominator has one more term of score 0: exp(s_j) / (1 + sum exp(s_j))
+      ``sink``         the softmax's denominator has one more term of score 0: exp(s_j) / (1 + sum exp(s_j));
+                       "learned": the term's score is a number per head, ``<prefix>.sink`` [heads], that is not
+                       scaled, capped or biased: exp(s_j) / (exp(sink_h) + sum exp(s_j))
+      ``softcap``      None | c: the scaled score becomes c tanh(score / c)
+      ``distance_bias``  None | e: slope_h * (i - j) is taken off the (capped) score of query i and key j,
+                       slope_h = 2^(-e (h + 1) / heads) for head h = 0 .. heads - 1
       ``names``        "proj" (default): ``<prefix>.{q,k,v,o}_proj.weight`` / ``.bias``;
                        "short": ``<prefix>.{q,k,v,o}`` and ``<prefix>.{q,k,v,o}.b``
       ``weights``      "softmax" (default) | "sigmoid": the weight of a visible key is sigmoid(score + pb[head]),
@@ -155,12 +165,18 @@ class AttentionMixer(Part):
         self.dim, self.vdim = self.hd, int(p.get("value_dim") or self.hd)      # sizes as the checkpoint has them
         self.norm_weighted = bool(p.get("qk_norm_weighted", False))
         self.sink = bool(p.get("sink", False))
+        self.learned_sink = p.get("sink") == "learned"
+        self.softcap = float(p["softcap"]) if p.get("softcap") else 0.0
+        self.distance_bias = float(p["distance_bias"]) if p.get("distance_bias") else None
+        self.sink_values = self.slopes = None
         self.sigmoid = p.get("weights", "softmax") == "sigmoid"
         if p.get("weights", "softmax") not in ("softmax", "sigmoid") or (self.sigmoid and self.sink):
             raise ValueError(f"{prefix}: weights are 'softmax' or 'sigmoid' (which has no sink)")
         self.value_rotation = dict(p["value_rotation"]) if p.get("value_rotation") else None
         if self.value_rotation and not self.sigmoid:
             raise ValueError(f"{prefix}: rotated values are built for sigmoid weights only")
+        if self.sigmoid and (self.softcap or self.distance_bias is not None):
+            raise ValueError(f"{prefix}: a cap or a distance bias on the scores is built for softmax weights only")
         self.head_bias = self._v_table = None
         self.short_names = p.get("names", "proj") == "short"
         if self.dim != self.vdim or self.dim % 16:
@@ -200,6 +216,8 @@ class AttentionMixer(Part):
             specs += [TensorSpec(f"{self.prefix}.{n}.norm", (self.dim,), init="ones") for n in "qk"]
         if self.sigmoid:
             specs.append(TensorSpec(f"{self.prefix}.pb", (self.nh,)))
+        if self.learned_sink:
+            specs.append(TensorSpec(f"{self.prefix}.sink", (self.nh,)))
         return specs
 
     def _pad_heads(self, t, heads: int, size: int):
@@ -236,6 +254,11 @@ class AttentionMixer(Part):
             self.w_qnorm, self.w_knorm = weight("q"), weight("k")
         if self.sigmoid:
             self.head_bias = fetch(f"{self.prefix}.pb").to(torch.float32).contiguous()
+        if self.learned_sink:
+            self.sink_values = fetch(f"{self.prefix}.sink").to(torch.float32).contiguous()
+        if self.distance_bias is not None:
+            slopes = [2.0 ** (-self.distance_bias * (h + 1) / self.nh) for h in range(self.nh)]
+            self.slopes = torch.tensor(slopes, dtype=torch.float64).to(torch.float32).to(self.w_qkv.device)
         if self.value_rotation:
             if self.vdim % 2:
                 raise ValueError(f"{self.prefix}: rotated values need an even value size")
@@ -270,7 +293,9 @@ class AttentionMixer(Part):
             o = sigmoid_attend_over_pages(q, cache.k_pages, cache.v_pages, block_table, ctx, self.nh, self.nkv, self.hd,
                                           chunk, sliding, self.scale, self.head_bias, self._v_table, v_inter)
             return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o, bias=self.b_o)
-        if self.hd == self.dim and ctx.max_new == 1 and cache.writes and self.FUSED_DECODE and qkv.dtype == torch.bfloat16:
+        extras = bool(self.softcap) or self.slopes is not None or self.sink_values is not None
+        if self.hd == self.dim and ctx.max_new == 1 and cache.writes and self.FUSED_DECODE and qkv.dtype == torch.bfloat16 \
+                and not extras:
             # a step of single decoded tokens: encoding, cache append, attention and the merge of its
             # splits in one launch, where the kernel takes the shapes
             o = ops.decode_attention_fused(qkv, self.nh, self.nkv, self.hd, positions, inv_freq, interleaved, self.qk_norm,
@@ -286,5 +311,6 @@ class AttentionMixer(Part):
                          k_norm_weight=self.w_knorm, norm_first=self.norm_weighted,
                          norm_dim=0 if plain else self.dim, rot_mul=rot_mul)
         o = attend_over_pages(q, cache.k_pages, cache.v_pages, block_table, ctx, self.nh, self.nkv, self.hd, chunk,
-                              sliding, self.scale, sink=self.sink)
+                              sliding, self.scale, sink=self.sink, softcap=self.softcap, slopes=self.slopes,
+                              sink_values=self.sink_values)
         return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o, bias=self.b_o)

@@ -8,7 +8,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from .context import GatedPending, Pending
+from .context import GatedPending, HyperPending, Pending
 from .linear import linear
 from .registry import BuildEnv, build, register
 from .spec import PartSpec, TensorSpec
@@ -46,27 +46,35 @@ class RMSNorm(Part):
     """y = x * rsqrt(mean(x^2) + eps) * w, statistics in float32
     (crates/hi-mlx/src/models.rs:1977-1979; crates/hi-cuda/src/kernels.cu:61-77).
     params: ``size``, ``eps``, ``name`` (tensor ``<prefix>.weight``; with ``tensor`` = "bare" the tensor
-    is ``<prefix>`` itself)."""
+    is ``<prefix>`` itself), ``one_plus`` (the tensor is stored around zero and acts as 1 + w; the sum is
+    taken in float32 and kept so).
+
+    Where the block keeps its residual stream as several copies (:class:`~hi_b200.parts.context.HyperPending`)
+    the norm reads the plain sum of the copies."""
 
     graph_safe = True
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
         self.size, self.eps = int(params["size"]), float(params["eps"])
+        self.one_plus = bool(params.get("one_plus", False))
         self.weight: Optional[torch.Tensor] = None
         self.tensor_name = prefix if params.get("tensor") == "bare" else f"{prefix}.weight"
 
     def tensor_specs(self):
-        return [TensorSpec(self.tensor_name, (self.size,), init="ones")]
+        return [TensorSpec(self.tensor_name, (self.size,), init="zeros" if self.one_plus else "ones")]
 
     def load(self, fetch):
-        self.weight = fetch(self.tensor_name).contiguous()
+        w = fetch(self.tensor_name)
+        self.weight = (w.to(torch.float32) + 1.0).contiguous() if self.one_plus else w.contiguous()
 
     def forward(self, residual: torch.Tensor, delta, row_map: Optional[torch.Tensor] = None, also_f32: bool = False,
                 out_dtype: Optional[torch.dtype] = None):
         """``delta``: None, a tensor, or a :class:`~hi_b200.parts.context.Pending`. ``out_dtype``: the engine's
         dtype, or float32 for a consumer that goes on in 32-bit."""
         out_dtype = out_dtype or self.env.dtype
+        if isinstance(delta, HyperPending):
+            return resolve_hyper(residual, delta, self.weight, self.eps, out_dtype, None, row_map, also_f32)
         if isinstance(delta, Pending):
             if delta.top_k > 8:
                 delta = delta.materialize(residual.shape[0])
@@ -301,8 +309,8 @@ class LinearHead(Part):
     """logits = z W^T in float32. The separate head is used when its tensor exists, else the
     embedding table (decided by presence, crates/hi-mlx/src/models.rs:6186-6193, 6211-6214).
     params: ``vocab_size``, ``hidden_size``, ``tie`` (random weights: write no head tensor),
-    ``softcap`` (None, or c: logits <- c tanh(logits / c)), ``tensor`` (the head tensor's whole name;
-    default ``<prefix>.weight``)."""
+    ``softcap`` (None, or c: logits <- c tanh(logits / c)), ``scale`` (a factor on the logits, default 1),
+    ``tensor`` (the head tensor's whole name; default ``<prefix>.weight``)."""
 
     graph_safe = True
 
@@ -311,6 +319,7 @@ class LinearHead(Part):
         self.weight: Optional[torch.Tensor] = None
         self.tied = False
         self.softcap = float(params["softcap"]) if params.get("softcap") else None
+        self.scale = float(params.get("scale", 1.0))
         self.tensor_name = params.get("tensor") or f"{prefix}.weight"
 
     def tensor_specs(self):
@@ -326,6 +335,8 @@ class LinearHead(Part):
     def forward(self, normed_rows: torch.Tensor, embedding: TokenEmbedding) -> torch.Tensor:
         w = embedding.table if self.weight is None else self.weight
         logits = linear(normed_rows, w, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            logits.mul_(self.scale)
         return logits if self.softcap is None else ops.softcap_(logits.contiguous(), self.softcap)
 
 
@@ -582,6 +593,108 @@ class ParallelConvBlock(Part):
         if isinstance(second, Pending):
             second = second.materialize(h_b.shape[0])
         return residual, Pending(dense=delta, dense2=second)
+
+
+def resolve_hyper(streams, pending, weight, eps, out_dtype, in_coef, row_map=None, also_f32=False):
+    """One boundary of a residual stream of several copies (``ops.hyper_step``): what ``pending`` (a
+    :class:`~hi_b200.parts.context.HyperPending` or None) holds enters the copies, and the weighted sum of the copies
+    (``in_coef``; None: the plain sum) is normed with ``weight``."""
+    if pending is None:
+        return ops.hyper_step(streams, weight, eps, out_dtype, in_coef=in_coef, row_map=row_map, also_f32=also_f32)
+    d = pending.delta
+    if isinstance(d, Pending):
+        return ops.hyper_step(streams, weight, eps, out_dtype, delta=d.dense, delta2=d.dense2, routed=d.routed,
+                              slot_of_entry=d.slot_of_entry, top_k=d.top_k, routed_weight=d.entry_weights,
+                              mix=pending.mix, out_coef=pending.out_coef, mult=pending.mult, in_coef=in_coef,
+                              row_map=row_map, also_f32=also_f32)
+    return ops.hyper_step(streams, weight, eps, out_dtype, delta=d, mix=pending.mix, out_coef=pending.out_coef,
+                          mult=pending.mult, in_coef=in_coef, row_map=row_map, also_f32=also_f32)
+
+
+@register("arrangement", "hyper_connections")
+class HyperConnectionBlock(Part):
+    """A pre-norm block whose residual stream is S copies x_1 .. x_S per token (all equal to the embedding output
+    before the first layer). Sub-layer q (1: mixer, 2: feed-forward) reads one weighted sum of the copies and its
+    result goes back into every copy while the copies are mixed among themselves:
+
+        u = sum_s in_q[s] x_s;   y = sublayer_q(norm_q(u));   x_t <- sum_s mix_q[s, t] x_s + mult * out_q[t] * y
+
+    for all t at once, from the old copies. Whoever reads the stream after the last layer takes the plain sum of
+    the copies. The copies are float32 [N, S, W]; every boundary between two sub-layers is one kernel
+    (``ops.hyper_step``): the update with the result the sub-layer before left, the next sub-layer's weighted sum and
+    its norm. The block hands the copies on as the stream with its last result as a
+    :class:`~hi_b200.parts.context.HyperPending`, as the pre-norm block hands on a ``Pending``.
+
+    params: ``hidden_size``, ``streams`` (S >= 1), ``mult`` (default 1), ``feed_forward`` (default True),
+    ``learned`` (default True; False: one copy, in = out = mix = 1: x <- x + mult * y, no tensors).
+    tensors: ``<prefix>.hc<q>.in`` [S], ``<prefix>.hc<q>.out`` [S], ``<prefix>.hc<q>.mix`` [S, S] ([from, to]).
+    The norms must be ``rmsnorm``."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        self.width, self.copies = int(params["hidden_size"]), int(params.get("streams", 1))
+        self.mult = float(params.get("mult", 1.0))
+        self.has_ff = bool(params.get("feed_forward", True))
+        self.learned = bool(params.get("learned", True))
+        if self.copies < 1 or self.copies > 16 or (not self.learned and self.copies != 1):
+            raise ValueError(f"{prefix}: {self.copies} copies of the stream are not supported (1 to 16; without "
+                             f"learned coefficients one)")
+        self.coef = {}
+
+    def _sublayers(self):
+        return (1, 2) if self.has_ff else (1,)
+
+    def tensor_specs(self):
+        if not self.learned:
+            return []
+        s, specs = self.copies, []
+        for q in self._sublayers():
+            specs += [TensorSpec(f"{self.prefix}.hc{q}.in", (s,), init="ones"),
+                      TensorSpec(f"{self.prefix}.hc{q}.out", (s,), init="ones"),
+                      TensorSpec(f"{self.prefix}.hc{q}.mix", (s, s))]
+        return specs
+
+    def load(self, fetch):
+        f32 = torch.float32
+        for q in self._sublayers():
+            if self.learned:
+                self.coef[q] = tuple(fetch(f"{self.prefix}.hc{q}.{n}").to(f32).contiguous() for n in ("in", "out", "mix"))
+            else:
+                one = torch.ones(1, dtype=f32, device=self.env.device)
+                self.coef[q] = (one, one, one.view(1, 1))
+
+    def forward(self, layer, residual, pending, ctx, cache_view):
+        norm1, norm2 = layer.norm_mixer, layer.norm_feed_forward
+        if not isinstance(norm1, RMSNorm) or (self.has_ff and not isinstance(norm2, RMSNorm)):
+            raise TypeError(f"{self.prefix}: the block works with rmsnorm norms")
+        in1, out1, mix1 = self.coef[1]
+        if residual.dim() == 2:
+            # the first layer: the copies do not exist yet; all of them are the stream as it comes
+            if pending is not None:
+                raise TypeError(f"{self.prefix}: the first block of copies cannot follow a block that leaves a sum open")
+            streams = torch.empty((residual.shape[0], self.copies, self.width), dtype=torch.float32, device=residual.device)
+            h = ops.hyper_step(streams, norm1.weight, norm1.eps, self.env.dtype, x_in=residual, in_coef=in1)
+        else:
+            if pending is not None and not isinstance(pending, HyperPending):
+                raise TypeError(f"{self.prefix}: the block before this one left a sum that is not for copies of the stream")
+            streams = residual
+            h = resolve_hyper(streams, pending, norm1.weight, norm1.eps, self.env.dtype, in1)
+        if ctx.tap is not None:
+            ctx.tap(f"{self.prefix}.stream_in", streams)        # debug: the copies as this layer reads them
+        y = layer.mixer.forward(h, ctx, cache_view)
+        pending = HyperPending(delta=y, mix=mix1, out_coef=out1, mult=self.mult)
+        if self.has_ff:
+            in2, out2, mix2 = self.coef[2]
+            if getattr(layer.feed_forward, "wants_f32_input", False):
+                h, h32 = resolve_hyper(streams, pending, norm2.weight, norm2.eps, self.env.dtype, in2, also_f32=True)
+                y = layer.feed_forward.forward(h, ctx, normed_f32=h32)
+            else:
+                h = resolve_hyper(streams, pending, norm2.weight, norm2.eps, self.env.dtype, in2)
+                y = layer.feed_forward.forward(h, ctx)
+            pending = HyperPending(delta=y, mix=mix2, out_coef=out2, mult=self.mult)
+        return streams, pending
 
 
 # --------------------------------------------------------------------------- between passes

@@ -101,3 +101,16 @@ class GatedPending:
     history: Optional[torch.Tensor] = None
     filled: int = 0
     mix: Optional[torch.Tensor] = None
+
+
+@dataclass
+class HyperPending:
+    """What a block with a residual stream of several copies leaves for the next norm: a sub-layer's result
+    (``delta``: a tensor or a :class:`Pending`) and the coefficients it enters the copies with,
+    x_t <- sum_s mix[s, t] x_s + mult * out_coef[t] * delta. The stream handed on beside it is the tensor of the
+    copies, float32 [N, S, W]; the norm that takes it updates them and reads its own input off them in one kernel."""
+
+    delta: object
+    mix: torch.Tensor            # float32 [S, S], indexed [from, to]
+    out_coef: torch.Tensor       # float32 [S]
+    mult: float = 1.0

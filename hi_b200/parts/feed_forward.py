@@ -114,7 +114,8 @@ class SigmoidRoutedExperts(Part):
     crates/hi-mlx/src/models.rs:6055-6103; the reference is top-1 only). The other routing rules of
     the reference's donor kernel (crates/hi-cuda/src/kernels.cu:536-546) are parameters too.
 
-    params: ``hidden_size``, ``num_experts``, ``top_k``, ``intermediate_size``, ``shared_expert``;
+    params: ``hidden_size``, ``num_experts``, ``top_k``, ``intermediate_size``, ``shared_expert``,
+      ``shared_intermediate_size`` (the shared expert's inner size; default ``intermediate_size``);
       ``score``        "sigmoid" (default) | "softmax" (over all experts)
       ``renormalize``  the chosen scores are divided by their sum (default False)
       ``scale``        "input" (default: the score multiplies what the expert reads) | "output"
@@ -127,7 +128,7 @@ class SigmoidRoutedExperts(Part):
       ``score_scale``  a constant factor on every chosen score (default 1)
       ``names``        "stacked" (default, the tensors below) | "per_expert": ``<prefix>.router`` [E, H] and for
                        every expert i ``<prefix>.e<i>.up`` [I, H], ``<prefix>.e<i>.down`` [H, I] (and ``.gate``
-                       with swiglu), stacked at load
+                       with swiglu), stacked at load; the shared expert is then ``<prefix>.shared.{gate,up,down}``
     tensors: ``<prefix>.router.weight`` [E, H]; ``<prefix>.experts.{gate,up}_proj.weight`` [E, I, H];
     ``<prefix>.experts.down_proj.weight`` [E, H, I]; ``<prefix>.shared_expert.{gate,up,down}_proj.weight``.
     """
@@ -145,8 +146,12 @@ class SigmoidRoutedExperts(Part):
         self.top_k, self.inter = int(params["top_k"]), int(params["intermediate_size"])
         if not 1 <= self.top_k <= self.experts:
             raise ValueError(f"{prefix}: top_k {self.top_k} outside 1..{self.experts}")
-        self.shared = _SwiGLU(f"{prefix}.shared_expert", self.hidden, self.inter) \
-            if params.get("shared_expert", True) else None
+        self.per_expert_names = params.get("names", "stacked") == "per_expert"
+        self.shared = None
+        if params.get("shared_expert", True):
+            shared_inter = int(params.get("shared_intermediate_size") or self.inter)
+            self.shared = _SwiGLU(f"{prefix}.shared", self.hidden, shared_inter, short_names=True) \
+                if self.per_expert_names else _SwiGLU(f"{prefix}.shared_expert", self.hidden, shared_inter)
         score, scale = params.get("score", "sigmoid"), params.get("scale", "input")
         if score not in ("sigmoid", "softmax") or scale not in ("input", "output"):
             raise ValueError(f"{prefix}: score {score!r} / scale {scale!r} are not known (sigmoid | softmax; input | output)")
@@ -165,7 +170,6 @@ class SigmoidRoutedExperts(Part):
                                  f"which {keep} hold {self.top_k} choices")
             self.router_mode |= ops.router_groups(count, keep)
         self.score_scale = float(params.get("score_scale", 1.0))
-        self.per_expert_names = params.get("names", "stacked") == "per_expert"
         self._ones: Optional[torch.Tensor] = None
         self.w_router = self.w_gate = self.w_up = self.w_down = None
         self._side_stream = None

@@ -8,7 +8,7 @@ import torch
 
 from ..kernels import ops
 from .attention import attend_over_pages
-from .basic import Part, exact_inverse_frequencies
+from .basic import Part, exact_inverse_frequencies, yarn_inverse_frequencies
 from .linear import linear
 from .registry import register
 from .spec import CacheSpec, TensorSpec
@@ -41,7 +41,11 @@ class LatentAttentionMixer(Part):
     norms), ``own_latents`` (False for a layer that reads another's), ``window`` (None | ("sliding", W) |
     ("chunk", C): which earlier latents a query reads; default all), ``gate`` (default True: the sigmoid gate
     per head), ``q_rank`` (default None: queries straight from h), ``rot_dim`` (default 0), ``rot_base``,
-    ``rot_scaling`` (None | the keys of :func:`~hi_b200.parts.basic.exact_inverse_frequencies`).
+    ``rot_scaling`` (None | the keys of :func:`~hi_b200.parts.basic.exact_inverse_frequencies`),
+    ``rot_kind`` ("llama3", the default | "yarn": ``rot_scaling`` = {factor, original, fast, slow}, the ramped
+    frequencies of :func:`~hi_b200.parts.basic.yarn_inverse_frequencies` and their factor on cos and sin, which
+    both the query's and the key's rotated part carry), ``rot_interleaved`` (pairs (2i, 2i + 1) instead of
+    (i, i + rot_dim/2)).
     tensors: ``<prefix>.q`` [heads*dim, H] (or ``<prefix>.dq`` [q_rank, H], ``<prefix>.dq.norm`` [q_rank],
     ``<prefix>.uq`` [heads*(dim+rot_dim), q_rank]), ``<prefix>.dkv`` [rank+rot_dim, H] and ``<prefix>.dkv.norm``
     [rank] (own latents only), ``<prefix>.uk`` [heads*dim, rank], ``<prefix>.uv`` [heads*vdim, rank],
@@ -70,8 +74,13 @@ class LatentAttentionMixer(Part):
         self.row_len = next((n for n in ops.TC_ROW_LENGTHS if need <= n), -(-need // 16) * 16)
         if self.row_len > 512:
             raise ValueError(f"{prefix}: kv_rank {self.rank} + rot_dim {self.rot} is not supported (up to 512)")
-        self._freq_host = None
-        if self.rot:
+        self._freq_host, self.rot_mul = None, 1.0
+        self.rot_interleaved = bool(p.get("rot_interleaved", False))
+        if p.get("rot_kind", "llama3") not in ("llama3", "yarn"):
+            raise ValueError(f"{prefix}: rot_kind is 'llama3' or 'yarn'")
+        if self.rot and p.get("rot_kind", "llama3") == "yarn":
+            self._freq_host, self.rot_mul = yarn_inverse_frequencies(self.rot, float(p["rot_base"]), p.get("rot_scaling"))
+        elif self.rot:
             self._freq_host = exact_inverse_frequencies(self.rot, float(p["rot_base"]), p.get("rot_scaling"))
         self._freq = None
         self.w_in = self.w_c = self.w_uk_t = self.w_uv_t = self.w_o = self.w_uq = self.w_qn = None
@@ -131,7 +140,7 @@ class LatentAttentionMixer(Part):
         off_kv = off_g + (self.heads if self.gate else 0)
         if self.own:
             ops.latent_append(proj[:, off_kv:], self.w_c, self.eps, ctx.positions, ctx.seq_of_token, block_table,
-                              cache.k_pages, inv_freq=self._freq)
+                              cache.k_pages, inv_freq=self._freq, interleaved=self.rot_interleaved, rot_mul=self.rot_mul)
         if self.q_rank:
             q = linear(ops.rmsnorm_rows(proj[:, : self.q_rank], self.w_qn, self.eps), self.w_uq)
         else:
@@ -142,7 +151,8 @@ class LatentAttentionMixer(Part):
         torch.bmm(q[:, :, : self.dim].transpose(0, 1), self.w_uk, out=q_lat.transpose(0, 1))
         if self.rot:
             # the rotated part of every head's query, turned by the token's position, behind its latent part
-            ops.rope_copy(q[:, :, self.dim:], q_lat[:, :, self.rank: self.rank + self.rot], ctx.positions, self._freq)
+            ops.rope_copy(q[:, :, self.dim:], q_lat[:, :, self.rank: self.rank + self.rot], ctx.positions, self._freq,
+                          interleaved=self.rot_interleaved, rot_mul=self.rot_mul)
         chunk = self.window[1] if self.window and self.window[0] == "chunk" else 0
         sliding = self.window[1] if self.window and self.window[0] == "sliding" else 0
         o_lat = attend_over_pages(q_lat, cache.k_pages, cache.k_pages, block_table, ctx, self.heads, 1, self.row_len,

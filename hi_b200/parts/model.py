@@ -11,6 +11,7 @@ from . import delta_rule as _delta     # noqa: F401
 from . import feed_forward as _ffn     # noqa: F401
 from . import gla as _gla              # noqa: F401
 from . import latent_attention as _latent  # noqa: F401
+from . import mamba2 as _mamba2         # noqa: F401
 from . import mlstm as _mlstm          # noqa: F401
 from . import pair as _pair            # noqa: F401
 from .context import CacheView, StepContext
