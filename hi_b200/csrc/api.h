@@ -52,8 +52,10 @@ int hb_attention_merge(const float* part_acc, const float* part_ml, void* out, i
 int hb_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                         int table_stride, const int* seq_of_token, const int* positions, void* out, int n_tokens,
                         int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int sink,
-                        const float* head_bias, int split_size, int max_splits, float* part_acc, float* part_ml,
+                        const float* head_bias, float softcap, const float* slopes, const float* sink_values,
+                        int split_size, int max_splits, float* part_acc, float* part_ml,
                         cudaStream_t stream);   // sink == 2: sigmoid weights with head_bias; plain sums go to part_acc
+                                                // softcap, slopes, sink_values: as hb_paged_attention
 
 int hb_attention_decode_tma(const void* q, const void* k_pages, const void* v_pages, int n_pages, const int* block_table,
                             int table_stride, const int* seq_of_token, const int* positions, void* out, int n_tokens,
@@ -76,6 +78,13 @@ int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages
                          int max_new, int nh, int nkv, int hd, int page_size, int chunk, int window, float scale,
                          int skip_single, int sink, cudaStream_t stream);
 
+// hb_attention_prefill_tc with reshaped scores: softcap, slopes, sink_values as hb_paged_attention
+int hb_attention_prefill_tc_reshaped(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                     int table_stride, const int* cu_seqlens, const int* positions, void* out,
+                                     int n_tokens, int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd,
+                                     int page_size, int chunk, int window, float scale, int skip_single, int sink,
+                                     float softcap, const float* slopes, const float* sink_values, int key_splits,
+                                     float* part_acc, float* part_ml, int* status, cudaStream_t stream);
 int hb_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                             int table_stride, const int* cu_seqlens, const int* positions, void* out, int n_tokens,
                             int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd, int page_size, int chunk,

@@ -55,8 +55,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table,
                    int table_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                    __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int chunk, int window,
-                   float scale, int sink, const float* __restrict__ head_bias, int split_size, int max_splits,
-                   float* __restrict__ part_acc, float* __restrict__ part_ml) {
+                   float scale, int sink, const float* __restrict__ head_bias, float softcap,
+                   const float* __restrict__ slopes, const float* __restrict__ sink_values, int split_size,
+                   int max_splits, float* __restrict__ part_acc, float* __restrict__ part_ml) {
+  // softcap > 0: a scaled score s becomes softcap * tanh(s / softcap); slopes [nh]: slopes[head] * (distance to the
+  // key) is taken off after the cap; sink_values [nh]: the sink's score is the head's own number instead of 0.
   // sink == 2: sigmoid weights. The weight of a key is sigmoid(score + head_bias[head]), nothing is normalised,
   // and every split's plain sum goes to part_acc (also when there is one split): the caller adds the splits.
   const bool sigmoid = sink == 2;
@@ -143,7 +146,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
     for (int e = 0; e < 4; ++e) o_acc[j][e] = 0.f;
   unsigned q_frag[HD / 16][4];
-  float row_bias[2] = {0.f, 0.f};
+  float row_bias[2] = {0.f, 0.f}, row_slope[2] = {0.f, 0.f};
+  if (slopes) {
+    if (lane / 4 < G) row_slope[0] = slopes[kvh * G + lane / 4];
+    if (lane / 4 + 8 < G) row_slope[1] = slopes[kvh * G + lane / 4 + 8];
+  }
+  const bool reshaped = softcap > 0.f || slopes != nullptr;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   if (sigmoid && head_bias) {
     if (lane / 4 < G) row_bias[0] = head_bias[kvh * G + lane / 4];
     if (lane / 4 + 8 < G) row_bias[1] = head_bias[kvh * G + lane / 4 + 8];
@@ -198,7 +207,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int key = key0 + nt * 8 + (e & 1);
-          const float v = key <= last ? s_acc[nt][e] * scale : -INFINITY;
+          float v = key <= last ? s_acc[nt][e] * scale : -INFINITY;
+          if (reshaped && key <= last) {
+            if (softcap > 0.f) v = softcap * tanhf(v * inv_cap);
+            v -= row_slope[e >> 1] * (float)(pos - key);
+          }
           s_acc[nt][e] = v;
           tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
         }
@@ -309,7 +322,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         ml[0] = mx; ml[1] = l;
       }
     } else {
-      if (sink && l > 0.f) l += expf(-mx);     // a key of score 0 without a value
+      // a key without a value, of score 0 or of the head's own score
+      if (sink && l > 0.f) l += expf((sink_values ? sink_values[kvh * G + row] : 0.f) - mx);
       out[(th0 + row) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     }
   }
@@ -319,7 +333,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 template <int HD>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
                   const int* seq_of_token, const int* positions, void* out, int n_tokens, int nh, int nkv,
-                  int page_size, int chunk, int window, float scale, int sink, const float* head_bias, int split_size,
+                  int page_size, int chunk, int window, float scale, int sink, const float* head_bias, float softcap,
+                  const float* slopes, const float* sink_values, int split_size,
                   int max_splits, float* part_acc, float* part_ml, cudaStream_t stream) {
   constexpr int STRIDE = HD + 8;
   const size_t smem = (size_t)(ROWS * STRIDE + 4 * TILE * STRIDE) * sizeof(__nv_bfloat16) +
@@ -330,8 +345,8 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
   dim3 grid(max_splits, nkv, n_tokens);
   attn_decode_kernel<HD><<<grid, NWARPS * 32, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_stride,
-      seq_of_token, positions, (__nv_bfloat16*)out, nh, nkv, page_size, chunk, window, scale, sink, head_bias, split_size,
-      max_splits, part_acc, part_ml);
+      seq_of_token, positions, (__nv_bfloat16*)out, nh, nkv, page_size, chunk, window, scale, sink, head_bias, softcap,
+      slopes, sink_values, split_size, max_splits, part_acc, part_ml);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }
@@ -344,8 +359,10 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
 extern "C" int hb_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                    int table_stride, const int* seq_of_token, const int* positions, void* out,
                                    int n_tokens, int nh, int nkv, int hd, int page_size, int chunk, int window,
-                                   float scale, int sink, const float* head_bias, int split_size, int max_splits,
+                                   float scale, int sink, const float* head_bias, float softcap, const float* slopes,
+                                   const float* sink_values, int split_size, int max_splits,
                                    float* part_acc, float* part_ml, cudaStream_t stream) {
+  if (sink == 2 && (softcap > 0.f || slopes || sink_values)) return HB_ERR_UNSUPPORTED;
   if (!q || !k_pages || !v_pages || !block_table || !seq_of_token || !positions || !out) return HB_ERR_BAD_ARG;
   if (n_tokens < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || table_stride <= 0 || chunk < 0 ||
       window < 0 || max_splits < 1 || split_size <= 0 || split_size % TILE != 0)
@@ -355,13 +372,13 @@ extern "C" int hb_attention_decode(const void* q, const void* k_pages, const voi
   if (n_tokens == 0) return HB_OK;
   if (hd == 192)
     return launch_decode<192>(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
-                              nh, nkv, page_size, chunk, window, scale, sink, head_bias, split_size, max_splits, part_acc, part_ml, stream);
+                              nh, nkv, page_size, chunk, window, scale, sink, head_bias, softcap, slopes, sink_values, split_size, max_splits, part_acc, part_ml, stream);
   if (hd == 128)
     return launch_decode<128>(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
-                              nh, nkv, page_size, chunk, window, scale, sink, head_bias, split_size, max_splits, part_acc, part_ml, stream);
+                              nh, nkv, page_size, chunk, window, scale, sink, head_bias, softcap, slopes, sink_values, split_size, max_splits, part_acc, part_ml, stream);
   if (hd == 64)
     return launch_decode<64>(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
-                             nh, nkv, page_size, chunk, window, scale, sink, head_bias, split_size, max_splits, part_acc, part_ml, stream);
+                             nh, nkv, page_size, chunk, window, scale, sink, head_bias, softcap, slopes, sink_values, split_size, max_splits, part_acc, part_ml, stream);
   return HB_ERR_UNSUPPORTED;
 }
 
@@ -435,7 +452,7 @@ extern "C" int hb_attention_decode_static(const void* q, const void* k_pages, co
     if (rc != HB_OK) return rc;
   }
   int rc = hb_attention_decode(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
-                               nh, nkv, hd, page_size, chunk, window, scale, 0, nullptr, split_size, max_splits, acc, ml, stream);
+                               nh, nkv, hd, page_size, chunk, window, scale, 0, nullptr, 0.f, nullptr, nullptr, split_size, max_splits, acc, ml, stream);
   if (rc != HB_OK || max_splits == 1 || n_tokens == 0) return rc;
   return hb_attention_merge(acc, ml, out, HB_DTYPE_BF16, n_tokens * nh, hd, max_splits, 0, nh, nullptr, stream);
 }

@@ -63,6 +63,12 @@ struct Args {
   // dims 2m, 2m + 1; else m, m + v_pairs with 2 * v_pairs == head_dim) turns by -position * v_inv_freq[m].
   int turn_inside, v_pairs, v_interleaved;
   const float* v_inv_freq;
+  // Scores reshaped before the softmax: softcap > 0: s <- softcap tanh(s / softcap) on the scaled score; slopes [nh]
+  // (or null): slopes[head] * (query position - key position) is taken off after the cap. sink_values [nh] (or
+  // null): with sink == 1 the extra term's score is the head's own number instead of 0.
+  float softcap;
+  const float* slopes;
+  const float* sink_values;
 };
 
 template <int HD>
@@ -251,6 +257,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int lo = first_visible(pos);
     float m = -INFINITY, l = 0.f;
     const float bias_log2 = (sigmoid && a.head_bias) ? a.head_bias[h] * 1.4426950408889634f : 0.f;
+    // reshaped scores are brought to units of log 2 first and the code below then takes them with a scale of one
+    const bool reshaped = a.softcap > 0.f || a.slopes != nullptr;
+    const float scale_l2 = reshaped ? 1.f : a.scale_log2;
+    const float slope_l2 = a.slopes ? a.slopes[h] * 1.4426950408889634f : 0.f;
+    const float cap_l2 = a.softcap * 1.4426950408889634f;
+    const float twice_over_cap = a.softcap > 0.f ? 2.f * a.scale_log2 / a.softcap : 0.f;
     bool ok = true;
     for (int j = 0; j < nt && ok; ++j) {
       const int sb = j & 1;
@@ -279,13 +291,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           sv[32 + i] = __uint_as_float(raw1[i]);
         }
       }
+      if (reshaped) {
+        // tanh(y) = 1 - 2 / (1 + e^(2 y)): one ex2 and one division per score
+        const float dist0 = (float)(pos - key_base);
+#pragma unroll
+        for (int i = 0; i < BKEYS; ++i) {
+          float x = sv[i] * a.scale_log2;
+          if (a.softcap > 0.f) x = cap_l2 * (1.f - __fdividef(2.f, 1.f + fast_exp2(sv[i] * twice_over_cap)));
+          sv[i] = x - slope_l2 * (dist0 - (float)i);
+        }
+      }
       if (interior && sigmoid) {
         // nothing to mask and no maximum to follow
       } else if (interior) {
         float top = -INFINITY;
 #pragma unroll
         for (int i = 0; i < BKEYS; ++i) top = fmaxf(top, sv[i]);
-        mx = fmaxf(mx, top * a.scale_log2);     // the scale is positive
+        mx = fmaxf(mx, top * scale_l2);     // the scale is positive
       } else {
 #pragma unroll
         for (int i = 0; i < BKEYS; ++i) {
@@ -293,7 +315,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           // masked scores become -inf BEFORE scaling, so the same exponential code serves both paths
           const float s = (row_ok && key <= pos && key >= lo) ? sv[i] : -INFINITY;
           sv[i] = s;
-          mx = fmaxf(mx, s * a.scale_log2);
+          mx = fmaxf(mx, s * scale_l2);
         }
       }
       // the S buffer may be overwritten by the MMA two tiles on
@@ -324,7 +346,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       } else {
         // two scores an instruction where the hardware has it (fma and add on pairs of floats);
         // the sum runs in four chains
-        const float2 scale2 = make_float2(a.scale_log2, a.scale_log2), neg_m2 = make_float2(-m, -m);
+        const float2 scale2 = make_float2(scale_l2, scale_l2), neg_m2 = make_float2(-m, -m);
         float2 part[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
         for (int i = 0; i < BKEYS; i += 4) {
@@ -479,7 +501,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
           }
         } else {
-        if (a.sink && l > 0.f) l += exp2f(-m);         // m is in units of log 2
+        if (a.sink && l > 0.f) l += exp2f((a.sink_values ? a.sink_values[h] * 1.4426950408889634f : 0.f) - m);   // m is in units of log 2
         const float inv = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* dst = a.out + ((size_t)(tok0 + r) * a.nh + h) * HD;
 #pragma unroll 1
@@ -545,7 +567,8 @@ int prefill_tc(const void* q, const void* k_pages, const void* v_pages, const in
                const int* cu_seqlens, const int* positions, void* out, int n_tokens, int n_pages, int n_seqs, int max_new,
                int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int skip_single, int sink,
                const float* head_bias, int key_splits, float* part_acc, float* part_ml, int* status, int turn_inside,
-               const float* v_inv_freq, int v_pairs, int v_interleaved, cudaStream_t stream);
+               const float* v_inv_freq, int v_pairs, int v_interleaved, float softcap, const float* slopes,
+               const float* sink_values, cudaStream_t stream);
 }  // namespace
 
 extern "C" int hb_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
@@ -556,7 +579,20 @@ extern "C" int hb_attention_prefill_tc(const void* q, const void* k_pages, const
                                        float* part_ml, int* status, cudaStream_t stream) {
   return prefill_tc(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_tokens, n_pages, n_seqs,
                     max_new, nh, nkv, hd, page_size, chunk, window, scale, skip_single, sink, head_bias, key_splits,
-                    part_acc, part_ml, status, 0, nullptr, 0, 0, stream);
+                    part_acc, part_ml, status, 0, nullptr, 0, 0, 0.f, nullptr, nullptr, stream);
+}
+
+// The same with reshaped scores (see Args): a cap, a distance bias per head, a sink with a score per head.
+extern "C" int hb_attention_prefill_tc_reshaped(const void* q, const void* k_pages, const void* v_pages,
+                                                const int* block_table, int table_stride, const int* cu_seqlens,
+                                                const int* positions, void* out, int n_tokens, int n_pages, int n_seqs,
+                                                int max_new, int nh, int nkv, int hd, int page_size, int chunk,
+                                                int window, float scale, int skip_single, int sink, float softcap,
+                                                const float* slopes, const float* sink_values, int key_splits,
+                                                float* part_acc, float* part_ml, int* status, cudaStream_t stream) {
+  return prefill_tc(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_tokens, n_pages, n_seqs,
+                    max_new, nh, nkv, hd, page_size, chunk, window, scale, skip_single, sink, nullptr, key_splits,
+                    part_acc, part_ml, status, 0, nullptr, 0, 0, softcap, slopes, sink_values, stream);
 }
 
 // Sigmoid weights with the result written by the kernel itself: `out` [n_tokens, nh, hd] bfloat16 takes every
@@ -573,7 +609,7 @@ extern "C" int hb_sigmoid_prefill_tc(const void* q, const void* k_pages, const v
   if (v_pairs > 0 && !v_interleaved && 2 * v_pairs != hd) return HB_ERR_UNSUPPORTED;
   return prefill_tc(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_tokens, n_pages, n_seqs,
                     max_new, nh, nkv, hd, page_size, chunk, window, scale, skip_single, 2, head_bias, 1, nullptr, nullptr,
-                    status, 1, v_inv_freq, v_pairs, v_interleaved, stream);
+                    status, 1, v_inv_freq, v_pairs, v_interleaved, 0.f, nullptr, nullptr, stream);
 }
 
 namespace {
@@ -581,7 +617,9 @@ int prefill_tc(const void* q, const void* k_pages, const void* v_pages, const in
                const int* cu_seqlens, const int* positions, void* out, int n_tokens, int n_pages, int n_seqs, int max_new,
                int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int skip_single, int sink,
                const float* head_bias, int key_splits, float* part_acc, float* part_ml, int* status, int turn_inside,
-               const float* v_inv_freq, int v_pairs, int v_interleaved, cudaStream_t stream) {
+               const float* v_inv_freq, int v_pairs, int v_interleaved, float softcap, const float* slopes,
+               const float* sink_values, cudaStream_t stream) {
+  if (sink == 2 && (softcap > 0.f || slopes || sink_values)) return HB_ERR_UNSUPPORTED;
   if (!q || !k_pages || !v_pages || !block_table || !cu_seqlens || !positions || !out || !status) return HB_ERR_BAD_ARG;
   if (n_tokens < 0 || n_pages <= 0 || n_seqs < 0 || max_new < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 ||
       page_size <= 0 || table_stride <= 0 || chunk < 0 || window < 0 || key_splits < 1 || key_splits > 64 ||
@@ -593,7 +631,7 @@ int prefill_tc(const void* q, const void* k_pages, const void* v_pages, const in
   if (n_seqs == 0 || max_new == 0 || n_tokens == 0) return HB_OK;
   Args a{block_table, cu_seqlens, positions, (__nv_bfloat16*)out, status, table_stride, nh, nkv, page_size, chunk,
          window, skip_single, page_size < BKEYS ? page_size : BKEYS, scale * 1.4426950408889634f, key_splits, part_acc, part_ml, sink, head_bias,
-         turn_inside, v_pairs, v_interleaved, v_inv_freq};
+         turn_inside, v_pairs, v_interleaved, v_inv_freq, softcap, slopes, sink_values};
   const long long pool_rows = (long long)n_pages * nkv * page_size;
   if (hd == 192) return launch<192>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
   if (hd == 128) return launch<128>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);

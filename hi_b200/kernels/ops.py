@@ -28,11 +28,13 @@ _SIGNATURES = {
     "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, I, I, F, P, I, I, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
     "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, F, P, P, I, I, P, P, P],
     "hb_attention_merge": [P, P, P, I, I, I, I, I, I, P, P],
-    "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, I, I, P, P, P],
+    "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, F, P, P, I, I, P, P, P],
     "hb_attention_decode_tma": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
     "hb_attention_decode_fused": [P, P, I, I, I, F, I, F, F, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P, P, I, F, I, P],
     "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
     "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P, I, P, P, P, P],
+    "hb_attention_prefill_tc_reshaped": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, F, P, P, I, P, P, P,
+                                         P],
     "hb_sigmoid_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P, I, I, P, P],
     "hb_sigmoid_merge": [P, P, P, I, I, P, I, I, I, I, I, P],
     "hb_router_topk": [P, I, P, I, I, I, I, I, I, F, P, P, P, P],
@@ -1060,8 +1062,8 @@ def sigmoid_decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: to
     part_acc = torch.empty((n, nh, splits, hd), dtype=torch.float32, device=q.device)
     _check(lib().hb_attention_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                                      _ptr(seq_of_token), _ptr(positions), _ptr(part_acc), n, nh, nkv, hd, page_size,
-                                     int(chunk), int(window), float(scale), 2, _ptr(head_bias), split_size, splits,
-                                     _ptr(part_acc), None, _stream()), "attention_decode")
+                                     int(chunk), int(window), float(scale), 2, _ptr(head_bias), 0.0, None, None, split_size,
+                                     splits, _ptr(part_acc), None, _stream()), "attention_decode")
     return sigmoid_merge(part_acc, positions, q.dtype, v_inv_freq, v_interleaved)
 
 
@@ -1140,10 +1142,12 @@ def decode_attention_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int)
 
 def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                      seq_of_token: torch.Tensor, positions: torch.Tensor, chunk: int, window: int, scale: float,
-                     max_context: int, sink: bool = False) -> torch.Tensor:
+                     max_context: int, sink: bool = False, softcap: float = 0.0,
+                     slopes: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention for a batch of single decoded tokens (every row of ``q`` is one request's
     token), bfloat16, split over runs of ``ATTENTION_SPLIT`` keys. Uses scratch memory for the
-    partial results of the splits."""
+    partial results of the splits. ``softcap``, ``slopes``, ``sink_values``: as :func:`paged_attention`
+    (the kernel that loads its tiles by cp.async takes them)."""
     _need(q, "q", torch.bfloat16); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
     for t, nm in ((block_table, "block_table"), (seq_of_token, "seq_of_token"), (positions, "positions")):
         _need(t, nm, torch.int32)
@@ -1164,15 +1168,23 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     if splits > 1:
         part_acc = torch.empty((n, nh, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n, nh, splits, 2), dtype=torch.float32, device=q.device)
+    reshaped = bool(softcap) or slopes is not None or sink_values is not None
+    for t, nm in ((slopes, "slopes"), (sink_values, "sink_values")):
+        if t is not None:
+            _need(t, nm, torch.float32)
+            if t.numel() != nh:
+                raise KernelError(f"{nm} needs one number per query head")
+    sink = bool(sink) or sink_values is not None
     # tile loads by TMA where the range and the pages allow it (the kernel says if not)
-    code = lib().hb_attention_decode_tma(_ptr(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
-                                         block_table.shape[1], _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv,
-                                         hd, page_size, int(chunk), int(window), float(scale), int(sink), split_size, splits,
-                                         _ptr(part_acc), _ptr(part_ml), _ptr(_tc_status(q.device)), _stream())
+    code = _UNSUPPORTED if reshaped else lib().hb_attention_decode_tma(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table), block_table.shape[1],
+        _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv, hd, page_size, int(chunk), int(window), float(scale),
+        int(sink), split_size, splits, _ptr(part_acc), _ptr(part_ml), _ptr(_tc_status(q.device)), _stream())
     if code == _UNSUPPORTED:
         code = lib().hb_attention_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                                          _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv, hd, page_size,
-                                         int(chunk), int(window), float(scale), int(sink), None, split_size, splits,
+                                         int(chunk), int(window), float(scale), int(sink), None, float(softcap),
+                                         _ptr(slopes), _ptr(sink_values), split_size, splits,
                                          _ptr(part_acc), _ptr(part_ml), _stream())
         _check(code, "attention_decode")
     else:
@@ -1180,7 +1192,7 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         _check(code, "attention_decode_tma")
     if splits > 1:
         _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, splits,
-                                        int(sink), nh, None, _stream()), "attention_merge")
+                                        int(sink), nh, _ptr(sink_values), _stream()), "attention_merge")
     return out
 
 
@@ -1308,10 +1320,13 @@ def prefill_attention_tc_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: 
 def prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                          cu_seqlens: torch.Tensor, positions: torch.Tensor, n_seqs: int, max_new: int, chunk: int,
                          window: int, scale: float, skip_single: bool = False,
-                         out: Optional[torch.Tensor] = None, key_splits: int = 1, sink: bool = False) -> torch.Tensor:
+                         out: Optional[torch.Tensor] = None, key_splits: int = 1, sink: bool = False,
+                         softcap: float = 0.0, slopes: Optional[torch.Tensor] = None,
+                         sink_values: Optional[torch.Tensor] = None) -> torch.Tensor:
     """As :func:`prefill_attention`, on tcgen05 (S, P V and O in tensor memory, TMA page loads).
     ``key_splits`` > 1: that many blocks share the key tiles of every (query tile, head) and a
-    merge kernel combines their rows (see :func:`prefill_key_splits`)."""
+    merge kernel combines their rows (see :func:`prefill_key_splits`). ``softcap``, ``slopes``, ``sink_values``:
+    as :func:`paged_attention`."""
     _need(q, "q", torch.bfloat16); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
     for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (positions, "positions")):
         _need(t, nm, torch.int32)
@@ -1330,18 +1345,31 @@ def prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
     if key_splits > 1:
         part_acc = torch.empty((n * nh, key_splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n * nh, key_splits, 2), dtype=torch.float32, device=q.device)
-    _check(lib().hb_attention_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
-                                         block_table.shape[1], _ptr(cu_seqlens), _ptr(positions), _ptr(out), n, n_pages,
-                                         n_seqs, int(max_new), nh, nkv, hd, page_size, int(chunk), int(window),
-                                         float(scale), int(skip_single), int(sink), None, key_splits,
-                                         _ptr(part_acc) if part_acc is not None else None,
-                                         _ptr(part_ml) if part_ml is not None else None, _ptr(_tc_status(q.device)),
-                                         _stream()),
-           "attention_prefill_tc")
+    for t, nm in ((slopes, "slopes"), (sink_values, "sink_values")):
+        if t is not None:
+            _need(t, nm, torch.float32)
+            if t.numel() != nh:
+                raise KernelError(f"{nm} needs one number per query head")
+    sink = bool(sink) or sink_values is not None
+    if softcap or slopes is not None or sink_values is not None:
+        _check(lib().hb_attention_prefill_tc_reshaped(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], _ptr(cu_seqlens),
+            _ptr(positions), _ptr(out), n, n_pages, n_seqs, int(max_new), nh, nkv, hd, page_size, int(chunk), int(window),
+            float(scale), int(skip_single), int(sink), float(softcap), _ptr(slopes), _ptr(sink_values), key_splits,
+            _ptr(part_acc), _ptr(part_ml), _ptr(_tc_status(q.device)), _stream()), "attention_prefill_tc")
+    else:
+        _check(lib().hb_attention_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                                             block_table.shape[1], _ptr(cu_seqlens), _ptr(positions), _ptr(out), n, n_pages,
+                                             n_seqs, int(max_new), nh, nkv, hd, page_size, int(chunk), int(window),
+                                             float(scale), int(skip_single), int(sink), None, key_splits,
+                                             _ptr(part_acc) if part_acc is not None else None,
+                                             _ptr(part_ml) if part_ml is not None else None, _ptr(_tc_status(q.device)),
+                                             _stream()),
+               "attention_prefill_tc")
     TC_USED[0] = True
     if key_splits > 1:
         _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, key_splits,
-                                        int(sink), nh, None, _stream()), "attention_merge")
+                                        int(sink), nh, _ptr(sink_values), _stream()), "attention_merge")
     return out
 
 

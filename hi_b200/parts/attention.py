@@ -40,9 +40,7 @@ def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, 
     (float32 [nh]): of the head's own score instead. ``softcap`` > 0: scores become softcap tanh(score / softcap);
     ``slopes`` (float32 [nh]): slopes[head] * (distance to the key) is taken off after the cap."""
     positions = ctx.positions
-    if softcap or slopes is not None or sink_values is not None:
-        return ops.paged_attention(q, k_pages, v_pages, block_table, ctx.seq_of_token, positions, chunk, sliding, scale,
-                                   ctx.max_context, sink=sink, softcap=softcap, slopes=slopes, sink_values=sink_values)
+    reshaped = bool(softcap) or slopes is not None or sink_values is not None
     # the decode kernel packs the query heads of one kv head into a 16-row tile; more heads on ONE shared kv
     # head go through it sixteen at a time
     per_call = nh if nkv > 1 or nh <= 16 else 16
@@ -51,27 +49,30 @@ def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, 
     def decode(rows_q, seq, pos, longest):
         if per_call == nh:
             return ops.decode_attention(rows_q, k_pages, v_pages, block_table, seq, pos, chunk, sliding, scale, longest,
-                                        sink=sink)
+                                        sink=sink, softcap=softcap, slopes=slopes, sink_values=sink_values)
         out = torch.empty_like(rows_q)
         for first in range(0, nh, per_call):
             part = rows_q[:, first: first + per_call].contiguous()
+            own = [None if t is None else t[first: first + per_call].contiguous() for t in (slopes, sink_values)]
             out[:, first: first + per_call] = ops.decode_attention(part, k_pages, v_pages, block_table, seq, pos, chunk,
-                                                                   sliding, scale, longest, sink=sink)
+                                                                   sliding, scale, longest, sink=sink, softcap=softcap,
+                                                                   slopes=own[0], sink_values=own[1])
         return out
 
     if ctx.max_new == 1 and decode_ok:
         # every token of the step is one request's decoded token: the tensor-core kernel
         return decode(q, ctx.seq_of_token, positions, ctx.max_context)
-    if ctx.max_new > 1 and ops.prefill_attention_supported(q.dtype, nh, nkv, hd):
+    # at least a tile of new tokens somewhere: the tcgen05 kernel; short portions: mma.sync, which takes no reshaped
+    # scores (a cap, a distance bias, a sink with a score of its own): those go to the general kernel below
+    tc = ctx.max_new >= ops.PREFILL_TC_MIN_TOKENS and ops.prefill_attention_tc_supported(q.dtype, nh, nkv, hd, ctx.page_size)
+    if ctx.max_new > 1 and ops.prefill_attention_supported(q.dtype, nh, nkv, hd) and (tc or not reshaped):
         # portions of prompts (single tokens of other requests ride along as one-row tiles)
         single = ctx.decode_rows is not None and decode_ok
-        # at least a tile of new tokens somewhere: the tcgen05 kernel; short portions: mma.sync
-        tc = ctx.max_new >= ops.PREFILL_TC_MIN_TOKENS and ops.prefill_attention_tc_supported(
-            q.dtype, nh, nkv, hd, ctx.page_size)
         if tc:
             o = ops.prefill_attention_tc(q, k_pages, v_pages, block_table, ctx.cu_seqlens, positions,
                                          ctx.n_seqs, ctx.max_new, chunk, sliding, scale, skip_single=single,
-                                         key_splits=_key_splits(ctx, nh, chunk, sliding, single, q.device), sink=sink)
+                                         key_splits=_key_splits(ctx, nh, chunk, sliding, single, q.device), sink=sink,
+                                         softcap=softcap, slopes=slopes, sink_values=sink_values)
         else:
             o = ops.prefill_attention(q, k_pages, v_pages, block_table, ctx.cu_seqlens, positions,
                                       ctx.n_seqs, ctx.max_new, chunk, sliding, scale, skip_single=single, sink=sink)
@@ -83,7 +84,8 @@ def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, 
             o.index_copy_(0, rows, od)
         return o
     return ops.paged_attention(q, k_pages, v_pages, block_table, ctx.seq_of_token, positions,
-                               chunk, sliding, scale, ctx.max_context, sink=sink)
+                               chunk, sliding, scale, ctx.max_context, sink=sink, softcap=softcap, slopes=slopes,
+                               sink_values=sink_values)
 
 
 def sigmoid_attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, hd: int, chunk: int,
