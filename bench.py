@@ -1189,6 +1189,234 @@ def case_surinex_step(tokens=2048, batch=8, context=4096, width=2048, heads=16, 
     torch.cuda.synchronize()
 
 
+# --------------------------------------------------------------------------- Bezasun beside the closest existing models
+def _bezasun_config(width, heads, ff, layers, vocab=32000, streams=4, window=4096):
+    """Layers in the order latent attention (heads of 128 + 64 rotated over a latent of 128, a window), Mamba-2 (twice
+    the width in heads of 128 over 128 state channels), attention (heads of 128, a quarter as many key heads, capped
+    scores, distance bias, learned sink); every layer with 8 experts of half the dense size, 2 a token, and a shared
+    expert of the same size; ``streams`` copies of the residual stream."""
+    moe = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 8, "top": 2}, "shared": {"ff": ff // 2}}
+    latent = {"type": "latent_attention", "mlp": moe, "mixer": {
+        "heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 128, "q_rank": width // 2, "scale": 192 ** -0.5,
+        "mask": {"size": window},
+        "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    mamba = {"type": "mamba2", "mlp": moe, "mixer": {"heads": 2 * width // 128, "vdim": 128, "state": 128, "groups": 4,
+                                                      "conv": 4, "norm_groups": 4}}
+    att = {"type": "attention", "mlp": moe, "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
+                                                      "scale": 128 ** -0.5, "softcap": 30.0, "q_temp": {"coef": 0.5, "every": 256}}}
+    order = [(latent, mamba, att)[i % 3] for i in range(layers)]
+    return {"architecture": "Bezasun", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.5},
+            "residual_mult": 0.7, "logit_scale": 2.0, "streams": streams, "layers": order}
+
+
+def case_bezasun(width=2048, heads=16, ff=8192, layers=6, tokens=2048, batch=8, context=4096):
+    """Prefill (one prompt of ``tokens`` in one step) and decode (``batch`` requests at ``context`` cached tokens,
+    captured steps) throughput of a Bezasun model with random weights beside Fidatar (the closest existing model:
+    attention with a sink in turn with a matrix memory, routed experts) and a dense Llama-4-shaped model of equal
+    width, depth and heads; then the new and the extended kernels alone beside their like kernels, with the bytes
+    that must move over the measured copy bandwidth. Markdown on standard output."""
+    import torch
+
+    from hi_b200.engine.core import Engine, StepEntry
+    from hi_b200.kernels import ops
+
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    g = torch.Generator().manual_seed(0)
+
+    def timed(fn, reps=5, flush_l2=True):
+        fn()
+        ts = []
+        for _ in range(reps):
+            if flush_l2:
+                flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2]
+
+    print(f"peaks: {pk['hbm_gbs']:.0f} GB/s copy, {pk['bf16_tflops']:.0f} TFLOP/s bf16 ({pk['source']}); "
+          f"width {width}, {heads} heads of 128, feed-forward {ff}, {layers} layers, bf16, random weights\n")
+    print("| model | prefill tokens/s | ms | decode tokens/s | ms/step | weights GB | launches/decode step |\n|---|---|---|---|---|---|---|")
+    for name, cfg in (("Bezasun", _bezasun_config(width, heads, ff, layers)), ("Fidatar", _fidatar_config(width, heads, ff, layers)),
+                      ("dense Llama-4 shape", _dense_llama_config(width, heads, ff, layers))):
+        eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", device=DEV, kv_page_size=PAGE,
+                                 kv_cache_tokens=batch * (context + 256) + tokens + 256, max_active_requests=batch + 1)
+        vocab = eng.vocab_size
+        weights = sum(2 * int(torch.Size(sp.shape).numel()) for sp in eng.model.tensor_specs() if sp.init != "absent") / 1e9
+        prompt = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+
+        def prefill():
+            eng.step([StepEntry("p", prompt, [tokens - 1])])
+            eng.finish("p")
+        t_pre = timed(prefill, reps=3)
+        for i in range(batch):
+            eng.assume_cached(i, context)
+        toks = torch.randint(0, vocab, (64, batch), generator=g).tolist()
+        turn = [0]
+
+        def decode():
+            eng.step([StepEntry(i, [toks[turn[0] % 64][i]], [0]) for i in range(batch)], borrow=True)
+            turn[0] += 1
+        for _ in range(4):
+            decode()
+        before = ops.LAUNCHES[0]
+        t_dec = timed(decode, reps=9, flush_l2=False)
+        launches = (ops.LAUNCHES[0] - before) // 10
+        print(f"| {name} | {tokens / t_pre * 1e3:,.0f} | {t_pre:.2f} | {batch / t_dec * 1e3:,.0f} | {t_dec:.3f} | {weights:.2f} | {launches} |")
+        del eng
+        torch.cuda.empty_cache()
+
+    # ---- kernels alone: bytes that must move over the time, against the copy peak
+    bf, f32 = torch.bfloat16, torch.float32
+    dg = torch.Generator(device=DEV).manual_seed(0)
+    rnd = lambda *shape, dt=bf: torch.randn(*shape, device=DEV, generator=dg).to(dt)
+    rows = []
+
+    def row(kind, name, ms, nbytes, note=""):
+        rows.append(f"| {kind} | {name} | {ms * 1e3:.1f} | {nbytes / 1e6:.1f} | {nbytes / ms / 1e6:,.0f} | "
+                    f"{nbytes / ms / 1e6 / pk['hbm_gbs']:.2f} | {note} |")
+
+    copies = 4
+    m_heads, m_state, m_groups, m_taps = 2 * width // 128, 128, 4, 4
+    inner, gn = m_heads * 128, m_groups * m_state
+    channels = inner + 2 * gn
+    nkv = max(1, heads // 4)
+    for n, seqs, what in ((tokens, 1, "prefill"), (batch, batch, "decode")):
+        cu = torch.arange(0, n + 1, n // seqs, dtype=torch.int32, device=DEV)
+        sot = torch.repeat_interleave(torch.arange(seqs, device=DEV), n // seqs).to(torch.int32)
+        slots = torch.arange(seqs, dtype=torch.int32, device=DEV)
+        # the boundary of a stream of copies beside the residual add + RMSNorm
+        streams, x = rnd(n, copies, width, dt=f32), rnd(n, width, dt=f32)
+        d1, w32, w = rnd(n, width), rnd(width, dt=f32), rnd(width)
+        mix, oc, ic = rnd(copies, copies, dt=f32), rnd(copies, dt=f32), rnd(copies, dt=f32)
+        ms = timed(lambda: ops.hyper_step(streams, w32, 1e-5, bf, delta=d1, mix=mix, out_coef=oc, mult=0.7, in_coef=ic))
+        row(what, f"boundary of {copies} copies: update, weighted sum, RMSNorm", ms, n * width * (copies * 8 + 2 + 2))
+        routed, slot = rnd(2 * n, width, dt=f32), torch.randperm(2 * n, device=DEV, generator=dg).to(torch.int32)
+        rw = torch.rand(2 * n, device=DEV, generator=dg)
+        ms = timed(lambda: ops.hyper_step(streams, w32, 1e-5, bf, delta=d1, routed=routed, slot_of_entry=slot, top_k=2,
+                                          routed_weight=rw, mix=mix, out_coef=oc, mult=0.7, in_coef=ic, also_f32=True))
+        row(what, "the same with two routed rows a token and a float32 copy of the output", ms, n * width * (copies * 8 + 2 + 8 + 2 + 4))
+        ms = timed(lambda: ops.add_rmsnorm(x, d1, w, 1e-5, bf))
+        row(what, "like: residual add + RMSNorm (one stream)", ms, n * width * (4 + 2 + 4 + 2))
+        ms = timed(lambda: ops.add_rmsnorm(x, d1, w, 1e-5, bf, None, True, routed, slot, 2, rw))
+        row(what, "like: the same with two routed rows and a float32 copy", ms, n * width * (4 + 2 + 8 + 4 + 2 + 4))
+        # Mamba-2 around its recurrence
+        proj = rnd(n, inner + channels + m_heads)
+        taps, cb = rnd(channels, m_taps, dt=f32), rnd(channels, dt=f32)
+        s_len = m_heads * m_state * 128
+        state = torch.zeros(seqs, s_len + (m_taps - 1) * channels, device=DEV)
+        dtb, alog, dsk = rnd(m_heads, dt=f32), rnd(m_heads, dt=f32) - 2.0, rnd(m_heads, dt=f32)
+        prep = lambda: ops.mamba2_prep(proj, inner, inner + channels, taps, cb, state, s_len, dtb, alog, cu, sot, slots,
+                                       m_heads, m_groups, m_state, 128)
+        ms = timed(prep)
+        row(what, "mamba2: convolution, silu, dt, decay; x, dt x, B, C to float32", ms,
+            n * (channels * 2 + (2 * inner + 2 * gn + m_heads * m_state) * 4))
+        xx, v, k, q, decay = prep()
+        ms = timed(lambda: ops.delta_conv_update(proj, inner, channels, m_taps, state, s_len, cu, slots))
+        row(what, "mamba2: the convolution's rows of the state", ms, seqs * (m_taps - 1) * channels * 8)
+        ms = timed(lambda: ops.delta_recurrence(q, k, v, None, decay, state, cu, slots, m_heads, m_groups, m_state, 128,
+                                                single_tokens=seqs == n, plain=True))
+        row(what, f"mamba2: recurrence ({m_heads} heads of 128 x 128)", ms, n * (2 * inner + 2 * gn + m_heads * m_state) * 4 + 2 * seqs * s_len * 4,
+            f"{n * m_heads * 128 * 128 * 2 * 2 / ms / 1e9:,.1f} TFLOP/s float32 of its own arithmetic")
+        hd16 = heads * 128
+        q2, k2, v2, dec2 = rnd(n, hd16, dt=f32), rnd(n, hd16, dt=f32), rnd(n, hd16, dt=f32), torch.rand(n, hd16, device=DEV)
+        st2 = torch.zeros(seqs, heads * 128 * 128, device=DEV)
+        beta = torch.rand(n, heads, device=DEV)
+        ms = timed(lambda: ops.delta_recurrence(q2, k2, v2, beta, dec2, st2, cu, slots, heads, heads, 128, 128, single_tokens=seqs == n))
+        row(what, f"like: delta rule recurrence ({heads} heads of 128 x 128)", ms, n * 4 * hd16 * 4 + 2 * seqs * heads * 128 * 128 * 4,
+            f"{n * heads * 128 * 128 * 2 * 3 / ms / 1e9:,.1f} TFLOP/s float32 of its own arithmetic")
+        o, wn = rnd(n, inner, dt=f32), rnd(inner)
+        ms = timed(lambda: ops.mamba2_out(o, xx, proj[:, :inner], dsk, wn, 1e-5, m_heads, 128, 4, bf))
+        row(what, "mamba2: skip, silu gate, grouped RMS norm", ms, n * inner * (4 + 4 + 2 + 2))
+        o2, wn2 = rnd(n, hd16, dt=f32), rnd(128)
+        ms = timed(lambda: ops.delta_out_norm(o2, proj[:, :hd16], wn2, 1e-5, 128, bf, gate_silu=True))
+        row(what, "like: delta rule output norm and silu gate", ms, n * hd16 * (4 + 2 + 2))
+    # attention with reshaped scores beside the plain softmax, a prompt of `tokens` and `batch` single tokens at `context`
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], device=DEV)
+    sinks = torch.randn(heads, device=DEV, generator=dg)
+    for n, seqs, ctx_len, what in ((tokens, 1, tokens, "prefill"), (batch, batch, context, "decode")):
+        per = -(-ctx_len // PAGE)
+        pages = seqs * per
+        pos = (torch.arange(n, device=DEV) if seqs == 1 else torch.full((n,), ctx_len - 1, device=DEV)).to(torch.int32)
+        sot = torch.repeat_interleave(torch.arange(seqs, device=DEV), n // seqs).to(torch.int32)
+        cu = torch.arange(0, n + 1, n // seqs, dtype=torch.int32, device=DEV)
+        table = torch.randperm(pages, device=DEV, generator=dg).to(torch.int32).view(seqs, per).contiguous()
+        kp, vp = rnd(pages, nkv, PAGE, 128), rnd(pages, nkv, PAGE, 128)
+        q = rnd(n, heads, 128)
+        pairs = n * (n + 1) // 2 if seqs == 1 else n * ctx_len
+        kv_bytes = (ctx_len if seqs == 1 else n * ctx_len) * nkv * 128 * 2 * 2 + n * heads * 128 * 4
+        kw = {"softcap": 30.0, "slopes": slopes, "sink_values": sinks}
+        if seqs == 1:
+            ms = timed(lambda: ops.prefill_attention_tc(q, kp, vp, table, cu, pos, 1, n, 0, 0, 128 ** -0.5, **kw))
+            row(what, "attention with cap, distance bias, learned sink: tcgen05 prefill", ms, kv_bytes, f"{pairs * heads * 128 * 4 / ms / 1e9:,.1f} TFLOP/s")
+            ms = timed(lambda: ops.prefill_attention_tc(q, kp, vp, table, cu, pos, 1, n, 0, 0, 128 ** -0.5, sink=True))
+            row(what, "like: softmax with a sink of score 0, tcgen05 prefill", ms, kv_bytes, f"{pairs * heads * 128 * 4 / ms / 1e9:,.1f} TFLOP/s")
+        else:
+            ms = timed(lambda: ops.decode_attention(q, kp, vp, table, sot, pos, 0, 0, 128 ** -0.5, ctx_len, **kw))
+            row(what, "attention with cap, distance bias, learned sink: decode kernel (cp.async tiles)", ms, kv_bytes)
+            ms = timed(lambda: ops.decode_attention(q, kp, vp, table, sot, pos, 0, 0, 128 ** -0.5, ctx_len, sink=True))
+            row(what, "like: softmax with a sink of score 0, decode kernel (TMA tiles)", ms, kv_bytes)
+        # latent rows with ramped frequencies and interleaved pairs
+        inv = torch.tensor([10000.0 ** (-2.0 * i / 64) for i in range(32)], device=DEV)
+        lat, wl = rnd(n, 128 + 64), rnd(128)
+        pool = torch.zeros(pages, 1, PAGE, 192, dtype=bf, device=DEV)
+        ms = timed(lambda: ops.latent_append(lat, wl, 1e-5, pos, sot, table, pool, inv_freq=inv, interleaved=True, rot_mul=1.2))
+        row(what, "latent: RMS norm + rotated key part (interleaved, factor) into its page", ms, n * 192 * 4)
+        ms = timed(lambda: ops.latent_append(lat, wl, 1e-5, pos, sot, table, pool, inv_freq=inv))
+        row(what, "like: the same in halves without a factor", ms, n * 192 * 4)
+    ops.check_tc_status()
+    print("\n| step | kernel | us | MB that must move | GB/s | of the copy peak | |\n|---|---|---|---|---|---|---|")
+    print("\n".join(rows))
+
+
+def case_bezasun_step(tokens=2048, batch=8, context=4096, width=2048, heads=16, ff=8192, layers=3):
+    """One Bezasun prompt step and two decode steps with every kernel launched on its own (no captured graph), three
+    layers (latent attention, Mamba-2, attention): for a launch list under ncu."""
+    import torch
+
+    from hi_b200.engine.core import Engine, StepEntry
+
+    eng = Engine.from_config(_bezasun_config(width, heads, ff, layers), seed=0, dtype="bfloat16", device=DEV, kv_page_size=PAGE,
+                             kv_cache_tokens=batch * (context + 256) + tokens + 256, max_active_requests=batch + 1,
+                             use_cuda_graphs=False)
+    g = torch.Generator().manual_seed(0)
+    for rep in range(2):
+        eng.step([StepEntry("p", torch.randint(0, eng.vocab_size, (tokens,), generator=g).tolist(), [tokens - 1])])
+        eng.finish("p")
+    for i in range(batch):
+        eng.assume_cached(i, context)
+    for _ in range(3):
+        eng.step([StepEntry(i, [int(torch.randint(0, eng.vocab_size, (1,), generator=g))], [0]) for i in range(batch)])
+    torch.cuda.synchronize()
+
+
+def case_bezasun_attention(tokens=2048, heads=16, reshaped=1):
+    """The tcgen05 prefill attention alone on one prompt of ``tokens``, with capped scores, a distance bias and a learned
+    sink (``reshaped`` = 1) or as the plain softmax with a sink of score 0: three launches, for a capture under ncu."""
+    import torch
+
+    from hi_b200.kernels import ops
+
+    bf = torch.bfloat16
+    dg = torch.Generator(device=DEV).manual_seed(0)
+    rnd = lambda *shape: torch.randn(*shape, device=DEV, generator=dg).to(bf)
+    nkv, per = max(1, heads // 4), -(-tokens // PAGE)
+    pos = torch.arange(tokens, device=DEV).to(torch.int32)
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device=DEV)
+    table = torch.randperm(per, device=DEV, generator=dg).to(torch.int32).view(1, per).contiguous()
+    kp, vp, q = rnd(per, nkv, PAGE, 128), rnd(per, nkv, PAGE, 128), rnd(tokens, heads, 128)
+    kw = {"sink": True}
+    if reshaped:
+        kw = {"softcap": 30.0, "slopes": torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], device=DEV),
+              "sink_values": torch.randn(heads, device=DEV, generator=dg)}
+    for _ in range(3):
+        ops.prefill_attention_tc(q, kp, vp, table, cu, pos, 1, tokens, 0, 0, 128 ** -0.5, **kw)
+    torch.cuda.synchronize()
+    ops.check_tc_status()
+
+
 # --------------------------------------------------------------------------- Fidatar beside the closest existing models
 def _fidatar_config(width, heads, ff, layers, vocab=32000, chunk=8192):
     """Layers in turn attention (heads of 128, a quarter as many key heads, chunks of 8,192, half of a head
@@ -1518,7 +1746,8 @@ CASES = {"sweep": case_sweep, "decode_timeline": case_decode_timeline, "prefill_
          "prefill_attention": case_prefill_attention, "decode_step": case_decode_step, "prefill_step": case_prefill_step,
          "vinurax": case_vinurax, "delta_recurrence": case_delta_recurrence,
          "vinurax_step": case_vinurax_step, "fidatar": case_fidatar, "fidatar_step": case_fidatar_step,
-         "mlstm_recurrence": case_mlstm_recurrence, "surinex": case_surinex, "surinex_step": case_surinex_step}
+         "mlstm_recurrence": case_mlstm_recurrence, "surinex": case_surinex, "surinex_step": case_surinex_step,
+         "bezasun": case_bezasun, "bezasun_step": case_bezasun_step, "bezasun_attention": case_bezasun_attention}
 
 
 if __name__ == "__main__":

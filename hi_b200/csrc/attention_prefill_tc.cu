@@ -69,6 +69,9 @@ struct Args {
   float softcap;
   const float* slopes;
   const float* sink_values;
+  // With a distance bias the newest keys score highest: the key tiles are then taken newest first, so that the running
+  // maximum is found in the first tiles and O is seldom rescaled (oldest first it would move with nearly every tile).
+  int newest_first;
 };
 
 template <int HD>
@@ -182,7 +185,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       auto load = [&](int j, uint8_t* dst, const CUtensorMap* map, uint64_t* full) {
         tc::mbar_expect_tx(full, KBYTES);
         for (int b = 0; b < boxes; ++b) {
-          const int key0 = (tile_begin + j) * BKEYS + b * a.box_rows;
+          const int key0 = (a.newest_first ? tile_begin + nt - 1 - j : tile_begin + j) * BKEYS + b * a.box_rows;
           const int page = key0 <= p_last ? table[key0 / a.page_size] : -1;
           // keys past the portion's last position (or without a page) are masked: any row will do
           const int row = page >= 0 ? (page * a.nkv + kvh) * a.page_size + key0 % a.page_size : 0;
@@ -272,7 +275,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         break;
       }
       tc::fence_after();
-      const int key_base = (tile_begin + j) * BKEYS;
+      const int key_base = (a.newest_first ? tile_begin + nt - 1 - j : tile_begin + j) * BKEYS;
       // a tile every row of this warp sees whole needs no masks (most tiles of a long prompt)
       const int warp_first_pos = p_first + quarter * 32;
       const bool interior = (quarter * 32 + 31 < n_valid) && (key_base + BKEYS - 1 <= warp_first_pos) &&
@@ -292,13 +295,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
       if (reshaped) {
-        // tanh(y) = 1 - 2 / (1 + e^(2 y)): one ex2 and one division per score
-        const float dist0 = (float)(pos - key_base);
+        // score' = cap tanh(score / cap) - slope * (pos - key), in units of log 2, with tanh(y) = 1 - 2 / (1 + e^(2 y)):
+        // one ex2, one reciprocal and three multiply-adds per score; the branches are outside the loops
+        const float base = cap_l2 - slope_l2 * (float)(pos - key_base);      // cap_l2 is 0 without a cap
+        if (a.softcap > 0.f) {
+          const float minus_two_cap = -2.f * cap_l2;
 #pragma unroll
-        for (int i = 0; i < BKEYS; ++i) {
-          float x = sv[i] * a.scale_log2;
-          if (a.softcap > 0.f) x = cap_l2 * (1.f - __fdividef(2.f, 1.f + fast_exp2(sv[i] * twice_over_cap)));
-          sv[i] = x - slope_l2 * (dist0 - (float)i);
+          for (int i = 0; i < BKEYS; ++i) {
+            float r;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + fast_exp2(sv[i] * twice_over_cap)));
+            sv[i] = fmaf(r, minus_two_cap, fmaf(slope_l2, (float)i, base));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < BKEYS; ++i) sv[i] = fmaf(sv[i], a.scale_log2, fmaf(slope_l2, (float)i, base));
         }
       }
       if (interior && sigmoid) {
@@ -399,7 +409,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tc::st32_nowait(tmem + lane_addr + sb * S_COLS, packed);
         tc::wait_st();
       }
-      if (tile_begin + j == p_last / BKEYS && (p_last + 1) % BKEYS != 0) {
+      if (key_base / BKEYS == p_last / BKEYS && (p_last + 1) % BKEYS != 0) {
         // Value rows of positions past the portion's end hold whatever the page held before
         // (another request's numbers, possibly not finite): P is zero there, but 0 x NaN is NaN.
         // Once the V tile has landed, the threads of those rows zero them.
@@ -631,7 +641,7 @@ int prefill_tc(const void* q, const void* k_pages, const void* v_pages, const in
   if (n_seqs == 0 || max_new == 0 || n_tokens == 0) return HB_OK;
   Args a{block_table, cu_seqlens, positions, (__nv_bfloat16*)out, status, table_stride, nh, nkv, page_size, chunk,
          window, skip_single, page_size < BKEYS ? page_size : BKEYS, scale * 1.4426950408889634f, key_splits, part_acc, part_ml, sink, head_bias,
-         turn_inside, v_pairs, v_interleaved, v_inv_freq, softcap, slopes, sink_values};
+         turn_inside, v_pairs, v_interleaved, v_inv_freq, softcap, slopes, sink_values, slopes ? 1 : 0};
   const long long pool_rows = (long long)n_pages * nkv * page_size;
   if (hd == 192) return launch<192>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
   if (hd == 128) return launch<128>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
