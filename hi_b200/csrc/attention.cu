@@ -13,7 +13,7 @@
 
 namespace {
 
-// DPL: output dimensions a lane holds; head_dim <= 32 * DPL (8: up to 256, 16: up to 512).
+// DPL: output dimensions a lane holds; head_dim <= 32 * DPL (8: up to 256, 16: up to 512, 32: up to 1024).
 template <typename T, int kMaxDimsPerLane>
 __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                                        const T* __restrict__ v_pages, const int* __restrict__ block_table,
@@ -200,8 +200,8 @@ extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages,
   if (n_tokens < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || table_stride <= 0 ||
       chunk < 0 || window < 0)
     return HB_ERR_BAD_ARG;
-  if (hd <= 0 || hd % 8 != 0 || hd > 512) return HB_ERR_UNSUPPORTED;
-  const bool wide = hd > 256;
+  if (hd <= 0 || hd % 8 != 0 || hd > 1024) return HB_ERR_UNSUPPORTED;
+  const bool wide = hd > 256, widest = hd > 512;
   if (n_tokens == 0) return HB_OK;
   const int warps_per_block = 4;
   const long long warps = (long long)n_tokens * nh * max_splits;
@@ -214,9 +214,11 @@ extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages,
       (T*)out, n_tokens, nh, nkv, hd, page_size, chunk, window, scale, sink, softcap, slopes, sink_values, split_size,   \
       max_splits, part_acc, part_ml)
   if (dtype == HB_DTYPE_F32) {
-    if (wide) HB_PAGED_ATTENTION(float, 16); else HB_PAGED_ATTENTION(float, 8);
+    if (widest) HB_PAGED_ATTENTION(float, 32); else if (wide) HB_PAGED_ATTENTION(float, 16); else HB_PAGED_ATTENTION(float, 8);
   } else if (dtype == HB_DTYPE_BF16) {
-    if (wide) HB_PAGED_ATTENTION(__nv_bfloat16, 16); else HB_PAGED_ATTENTION(__nv_bfloat16, 8);
+    if (widest) HB_PAGED_ATTENTION(__nv_bfloat16, 32);
+    else if (wide) HB_PAGED_ATTENTION(__nv_bfloat16, 16);
+    else HB_PAGED_ATTENTION(__nv_bfloat16, 8);
   } else {
     return HB_ERR_BAD_ARG;
   }

@@ -90,6 +90,84 @@ __global__ void mamba2_prep_kernel(const MambaPrepArgs a) {
   }
 }
 
+// The same for sizes and offsets that are multiples of four: a thread takes four neighbouring channels of a unit with
+// one 8-byte (bfloat16) or 16-byte load per tap row, and writes 16 bytes at a time.
+__device__ __forceinline__ float4 ld4(const void* p, int dtype, size_t i) {
+  if (dtype == HB_DTYPE_F32) return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+  const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+  return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                     __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+}
+
+template <int KT>      // taps known at compile time (0: any number)
+__global__ void mamba2_prep_vec_kernel(const MambaPrepArgs a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int t = blockIdx.x;
+  const int s = a.seq_of_token[t];
+  const int start = a.cu_seqlens[s];
+  const int local = t - start;
+  const int inner = a.heads * a.vdim, gn = a.groups * a.n_state, C = inner + 2 * gn;
+  const int K = KT ? KT : a.K;
+  const float* conv = a.state + (size_t)a.slots[s] * a.state_stride + a.conv_off;   // [K-1, C]
+  const int units = a.heads + 2 * a.groups;
+  for (int u = blockIdx.y * warps + warp; u < units; u += gridDim.y * warps) {
+    const bool is_x = u < a.heads;
+    const int len = is_x ? a.vdim : a.n_state;
+    const int c0 = is_x ? u * a.vdim : inner + (u - a.heads) * a.n_state;
+    float dt = 0.f;
+    if (is_x) {
+      const float z = ldf(a.proj, a.proj_dtype, (size_t)t * a.ld + a.dt_off + u) + a.dt_bias[u];
+      dt = z > 20.f ? z : log1pf(expf(z));
+      const float g = expf(-expf(a.a_log[u]) * dt);
+      const float4 g4 = make_float4(g, g, g, g);
+      float4* dst = reinterpret_cast<float4*>(a.decay + ((size_t)t * a.heads + u) * a.n_state);
+      for (int i = lane; i < a.n_state / 4; i += 32) dst[i] = g4;
+    }
+    for (int i = lane * 4; i < len; i += 128) {
+      const int c = c0 + i;
+      float4 acc = *reinterpret_cast<const float4*>(a.conv_bias + c);
+      if (KT == 4) {
+        // four taps: a channel's taps are one 16-byte load, and all four rows are asked for before the first is used
+        float4 tp[4], xin[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) tp[e] = *reinterpret_cast<const float4*>(a.taps + (size_t)(c + e) * 4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int rel = local - 3 + j;
+          xin[j] = rel >= 0 ? ld4(a.proj, a.proj_dtype, (size_t)(start + rel) * a.ld + a.chan_off + c)
+                            : *reinterpret_cast<const float4*>(conv + (size_t)(3 + rel) * C + c);
+        }
+        acc.x += tp[0].x * xin[0].x + tp[0].y * xin[1].x + tp[0].z * xin[2].x + tp[0].w * xin[3].x;
+        acc.y += tp[1].x * xin[0].y + tp[1].y * xin[1].y + tp[1].z * xin[2].y + tp[1].w * xin[3].y;
+        acc.z += tp[2].x * xin[0].z + tp[2].y * xin[1].z + tp[2].z * xin[2].z + tp[2].w * xin[3].z;
+        acc.w += tp[3].x * xin[0].w + tp[3].y * xin[1].w + tp[3].z * xin[2].w + tp[3].w * xin[3].w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j < K) {
+            const int rel = local - (K - 1) + j;
+            const float4 xin = rel >= 0 ? ld4(a.proj, a.proj_dtype, (size_t)(start + rel) * a.ld + a.chan_off + c)
+                                        : *reinterpret_cast<const float4*>(conv + (size_t)(K - 1 + rel) * C + c);
+            acc.x += a.taps[(size_t)c * K + j] * xin.x;
+            acc.y += a.taps[(size_t)(c + 1) * K + j] * xin.y;
+            acc.z += a.taps[(size_t)(c + 2) * K + j] * xin.z;
+            acc.w += a.taps[(size_t)(c + 3) * K + j] * xin.w;
+          }
+        }
+      }
+      const float4 y = make_float4(silu1(acc.x), silu1(acc.y), silu1(acc.z), silu1(acc.w));
+      if (is_x) {
+        *reinterpret_cast<float4*>(a.x + (size_t)t * inner + c) = y;
+        *reinterpret_cast<float4*>(a.v + (size_t)t * inner + c) = make_float4(dt * y.x, dt * y.y, dt * y.z, dt * y.w);
+      } else if (c < inner + gn) {
+        *reinterpret_cast<float4*>(a.k + (size_t)t * gn + (c - inner)) = y;
+      } else {
+        *reinterpret_cast<float4*>(a.q + (size_t)t * gn + (c - inner - gn)) = y;
+      }
+    }
+  }
+}
+
 // grid (tokens, parts); a block norms one run of inner / parts channels.
 template <typename T>
 __global__ void mamba2_out_kernel(const float* __restrict__ o, const float* __restrict__ x, const void* __restrict__ z,
@@ -132,9 +210,17 @@ extern "C" int hb_mamba2_prep(const void* proj, int proj_dtype, long long ld, in
   a.q = q; a.decay = decay; a.heads = heads; a.groups = groups; a.n_state = n_state; a.vdim = vdim; a.K = taps_n;
   const int units = heads + 2 * groups;
   const int warps = units < 4 ? units : 4;
+  // a block finds its request's rows once and then takes units in turn: with many tokens few blocks a token, so
+  // that the look-ups are shared by more work; with few tokens a block per group of units, to fill the GPU
   int gy = (units + warps - 1) / warps;
+  const int want = (148 * 8 + n_tokens - 1) / n_tokens;
+  if (gy > want) gy = want;
   if (gy > 64) gy = 64;
-  mamba2_prep_kernel<<<dim3(n_tokens, gy), warps * 32, 0, stream>>>(a);
+  const bool vec = conv_bias && vdim % 4 == 0 && n_state % 4 == 0 && ld % 4 == 0 && chan_off % 4 == 0 && conv_off % 4 == 0 &&
+                   state_stride % 4 == 0 && taps_n <= 8;
+  if (vec && taps_n == 4) mamba2_prep_vec_kernel<4><<<dim3(n_tokens, gy), warps * 32, 0, stream>>>(a);
+  else if (vec) mamba2_prep_vec_kernel<0><<<dim3(n_tokens, gy), warps * 32, 0, stream>>>(a);
+  else mamba2_prep_kernel<<<dim3(n_tokens, gy), warps * 32, 0, stream>>>(a);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }

@@ -868,8 +868,8 @@ def qkv_post(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positions: torch.Ten
         raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {(nh + 2 * nkv) * hd}")
     general = v_inv_freq is not None or norm_first or q_norm_weight is not None or k_norm_weight is not None or rot_mul != 1.0 or \
         (norm_dim not in (0, hd)) or (inv_freq is not None and inv_freq.numel() % 8 != 0)
-    if hd % 8 != 0 or hd > 512 or (not general and (hd % 16 != 0 or hd > 256)):
-        raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 256; the general form: of 8 up to 512)")
+    if hd % 8 != 0 or hd > 1024 or (not general and (hd % 16 != 0 or hd > 256)):
+        raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 256; the general form: of 8 up to 1024)")
     v_pairs = 0
     if v_inv_freq is not None:
         _need(v_inv_freq, "v_inv_freq", torch.float32)
@@ -944,8 +944,8 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         raise KernelError("cache pages do not match the query's head_dim")
     if nh % nkv:
         raise KernelError(f"{nh} query heads are not a multiple of {nkv} kv heads")
-    if hd % 16 != 0 or hd > 512:
-        raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 512)")
+    if hd % 16 != 0 or hd > 1024:
+        raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 1024)")
     for t, nm in ((slopes, "slopes"), (sink_values, "sink_values")):
         if t is not None:
             _need(t, nm, torch.float32)

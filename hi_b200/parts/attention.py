@@ -183,7 +183,7 @@ class AttentionMixer(Part):
         self.short_names = p.get("names", "proj") == "short"
         if self.dim != self.vdim or self.dim % 16:
             self.hd = -(-max(self.dim, self.vdim) // 16) * 16                  # rows of the cache and of q
-        if self.hd > (512 if self.hd != self.dim or self.norm_weighted else 256):
+        if self.hd > (1024 if self.hd != self.dim or self.norm_weighted else 256):
             raise ValueError(f"{prefix}: head size {self.hd} is not supported")
         self.window = tuple(p["window"]) if p.get("window") else None
         self.position = build("position", p.get("position") or PartSpec("none"), env, prefix)

@@ -72,8 +72,8 @@ class LatentAttentionMixer(Part):
         # the cached row: padded with zeros to a length the tensor-core kernels take (64, 128, 192), else to 16s
         need = self.rank + self.rot
         self.row_len = next((n for n in ops.TC_ROW_LENGTHS if need <= n), -(-need // 16) * 16)
-        if self.row_len > 512:
-            raise ValueError(f"{prefix}: kv_rank {self.rank} + rot_dim {self.rot} is not supported (up to 512)")
+        if self.row_len > 1024:
+            raise ValueError(f"{prefix}: kv_rank {self.rank} + rot_dim {self.rot} is not supported (up to 1024)")
         self._freq_host, self.rot_mul = None, 1.0
         self.rot_interleaved = bool(p.get("rot_interleaved", False))
         if p.get("rot_kind", "llama3") not in ("llama3", "yarn"):

@@ -96,7 +96,13 @@ BZ_E = config(150, 64, 1e-5, [
     latent(2, 16, 16, 16, 200, 32, 0.15, 1000.0, mlp=moe(3, 1, 40)),
 ], streams=1, mult=0.9, logit_scale=3.0)
 
-CONFIGS = {"A": BZ_A, "B": BZ_B, "C": BZ_C, "D": BZ_D, "E": BZ_E}
+# rows wider than 512: a latent of 600 under two heads, attention heads of 320 with values of 48, two copies
+BZ_F = config(90, 40, 1e-5, [
+    latent(2, 24, 8, 16, 600, 16, 0.18, 10000.0, window=50, mlp=moe(2, 1, 12)),
+    attention(2, 1, 320, 48, 0.06, softcap=12.0, mlp=moe(2, 2, 12, shared=8)),
+], streams=2, mult=0.8)
+
+CONFIGS = {"A": BZ_A, "B": BZ_B, "C": BZ_C, "D": BZ_D, "E": BZ_E, "F": BZ_F}
 
 
 def peaked(cfg: dict, factor: float) -> dict:
