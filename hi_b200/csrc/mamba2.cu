@@ -190,6 +190,40 @@ __global__ void mamba2_out_kernel(const float* __restrict__ o, const float* __re
   }
 }
 
+// The same with four channels a thread and the gated row kept in shared memory between the two passes, so that o, x
+// and z are read once: for runs that are a multiple of four and fit there.
+template <typename T>
+__global__ void mamba2_out_vec_kernel(const float* __restrict__ o, const float* __restrict__ x, const void* __restrict__ z,
+                                      int z_dtype, long long z_stride, const float* __restrict__ d_skip,
+                                      const T* __restrict__ w, float eps, T* __restrict__ out, int inner, int vdim, int run) {
+  __shared__ float scratch[33];
+  extern __shared__ float4 y_s[];      // [run / 4]
+  const size_t t = blockIdx.x;
+  const int c0 = blockIdx.y * run;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < run; i += blockDim.x * 4) {
+    const int c = c0 + i;
+    const float4 ov = *reinterpret_cast<const float4*>(o + t * inner + c);
+    const float4 xv = *reinterpret_cast<const float4*>(x + t * inner + c);
+    const float4 zv = ld4(z, z_dtype, t * z_stride + c);
+    const float d = d_skip[c / vdim];                      // four neighbours lie in one head (vdim % 4 == 0)
+    const float4 y = make_float4((ov.x + d * xv.x) * silu1(zv.x), (ov.y + d * xv.y) * silu1(zv.y),
+                                 (ov.z + d * xv.z) * silu1(zv.z), (ov.w + d * xv.w) * silu1(zv.w));
+    y_s[i >> 2] = y;
+    ss += y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
+  }
+  const float inv = rsqrtf(hb::block_sum(ss, scratch) / (float)run + eps);
+  for (int i = threadIdx.x * 4; i < run; i += blockDim.x * 4) {
+    const int c = c0 + i;
+    const float4 y = y_s[i >> 2];
+    T* dst = out + t * inner + c;
+    dst[0] = hb::from_f32<T>(y.x * inv * hb::to_f32(w[c]));
+    dst[1] = hb::from_f32<T>(y.y * inv * hb::to_f32(w[c + 1]));
+    dst[2] = hb::from_f32<T>(y.z * inv * hb::to_f32(w[c + 2]));
+    dst[3] = hb::from_f32<T>(y.w * inv * hb::to_f32(w[c + 3]));
+  }
+}
+
 }  // namespace
 
 extern "C" int hb_mamba2_prep(const void* proj, int proj_dtype, long long ld, int chan_off, int dt_off, const float* taps,
@@ -236,6 +270,19 @@ extern "C" int hb_mamba2_out(const float* o, const float* x, const void* z, int 
   const int run = inner / parts;
   const int threads = run >= 1024 ? 256 : (run >= 128 ? 128 : (run + 31) / 32 * 32);
   const dim3 grid(n_tokens, parts);
+  if (vdim % 4 == 0 && run % 4 == 0 && z_stride % 4 == 0 && (size_t)run * 4 <= 48 * 1024 &&
+      (dtype == HB_DTYPE_F32 || dtype == HB_DTYPE_BF16)) {
+    const int vthreads = run >= 1024 ? 256 : (run >= 512 ? 128 : (run / 4 + 31) / 32 * 32);
+    const size_t smem = (size_t)run * sizeof(float);
+    if (dtype == HB_DTYPE_F32)
+      mamba2_out_vec_kernel<float><<<grid, vthreads, smem, stream>>>(o, x, z, z_dtype, z_stride, d_skip, (const float*)w, eps,
+                                                                     (float*)out, inner, vdim, run);
+    else
+      mamba2_out_vec_kernel<__nv_bfloat16><<<grid, vthreads, smem, stream>>>(
+          o, x, z, z_dtype, z_stride, d_skip, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)out, inner, vdim, run);
+    HB_LAUNCH_CHECK();
+    return HB_OK;
+  }
   if (dtype == HB_DTYPE_F32)
     mamba2_out_kernel<float><<<grid, threads, 0, stream>>>(o, x, z, z_dtype, z_stride, d_skip, (const float*)w, eps,
                                                            (float*)out, inner, vdim, run);
