@@ -374,6 +374,23 @@ def test_other_page_sizes_and_kernel_choices(models):
             assert every <= used, sorted(every - used)
 
 
+def test_long_portions_beside_single_tokens(models):
+    """Portions of a tile of new tokens and more (the tcgen05 kernel) in one step with single decoded tokens of other
+    requests (the decode kernel), pages of 64: attention with reshaped scores over heads of 64 and latent rows of 128."""
+    cfg, mdir, weights = models["B"]
+    requests = {"a": tokens(cfg, 420, 31), "b": tokens(cfg, 200, 32), "c": tokens(cfg, 170, 33)}
+    a, b, c = requests["a"], requests["b"], requests["c"]
+    steps = [([("b", b[:60], list(range(60)))], []),
+             ([("a", a[:150], list(range(150))), ("b", b[60:61], [0])], []),
+             ([("a", a[150:300], list(range(150))), ("b", b[61:62], [0]), ("c", c[:129], list(range(129)))], []),
+             ([("b", b[62:200], list(range(138))), ("a", a[300:301], [0]), ("c", c[129:130], [0])], ["b"]),
+             ([("a", a[301:420], list(range(119))), ("c", c[130:170], list(range(40)))], ["a", "c"])]
+    for dtype in ("float32", "bfloat16"):
+        eng = engine(mdir, dtype, kv_page_size=64, kv_cache_tokens=1024)
+        got, forced = replay(eng, steps, dtype)
+        compare(cfg, weights, requests, got, TOL[dtype], f"long portions beside single tokens {dtype}", forced)
+
+
 @pytest.mark.parametrize("name", ["A", "C", "D"])
 def test_greedy_generation_through_the_entry_point(name, models):
     """hi_b200.generate (scheduler, sampler, launch-ahead) against greedy decoding of the plain model."""
