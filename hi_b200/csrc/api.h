@@ -73,6 +73,12 @@ int hb_attention_decode_fused(const void* qkv, const float* inv_freq, int rot_pa
                               const float* q_norm_w, const float* k_norm_w, int norm_first, float rot_mul, int sink,
                               cudaStream_t stream);
 
+// hb_attention_prefill with reshaped scores: softcap, slopes, sink_values as hb_paged_attention
+int hb_attention_prefill_reshaped(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                  int table_stride, const int* cu_seqlens, const int* positions, void* out, int n_seqs,
+                                  int max_new, int nh, int nkv, int hd, int page_size, int chunk, int window, float scale,
+                                  int skip_single, int sink, float softcap, const float* slopes, const float* sink_values,
+                                  cudaStream_t stream);
 int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                          int table_stride, const int* cu_seqlens, const int* positions, void* out, int n_seqs,
                          int max_new, int nh, int nkv, int hd, int page_size, int chunk, int window, float scale,

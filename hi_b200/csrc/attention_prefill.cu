@@ -23,7 +23,10 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table,
                     int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
                     __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int chunk, int window,
-                    float scale, int skip_single, int sink) {
+                    float scale, int skip_single, int sink, float softcap, const float* __restrict__ slopes,
+                    const float* __restrict__ sink_values) {
+  // softcap > 0: a scaled score s becomes softcap * tanh(s / softcap); slopes [nh]: slopes[head] * (distance to the
+  // key) is taken off after the cap; sink_values [nh]: the sink's score is the head's own number instead of 0.
   constexpr int STRIDE = HD + 8;
   constexpr int CHUNKS = HD / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -100,6 +103,10 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int lo_a = first_visible(pos_a), lo_b = first_visible(pos_b);
   const bool ok_a = ra < n_valid, ok_b = rb < n_valid;
 
+  const bool reshaped = softcap > 0.f || slopes != nullptr;
+  const float slope = slopes ? slopes[h] : 0.f;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o_acc[HD / 8][4];
 #pragma unroll
@@ -152,7 +159,11 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
           const int key = key0 + nt * 8 + (e & 1);
           const bool second = e >> 1;
           const bool vis = second ? (ok_b && key <= pos_b && key >= lo_b) : (ok_a && key <= pos_a && key >= lo_a);
-          const float v = vis ? s_acc[nt][e] * scale : -INFINITY;
+          float v = vis ? s_acc[nt][e] * scale : -INFINITY;
+          if (reshaped && vis) {
+            if (softcap > 0.f) v = softcap * tanhf(v * inv_cap);
+            v -= slope * (float)((second ? pos_b : pos_a) - key);
+          }
           s_acc[nt][e] = v;
           tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
         }
@@ -208,9 +219,10 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     }
     __syncthreads();
   }
-  if (sink) {      // one more term of score 0 in the denominator; it has no value
-    if (l_run[0] > 0.f) l_run[0] += expf(-m_run[0]);
-    if (l_run[1] > 0.f) l_run[1] += expf(-m_run[1]);
+  if (sink) {      // one more term in the denominator, of score 0 or of the head's own score; it has no value
+    const float sv = sink_values ? sink_values[h] : 0.f;
+    if (l_run[0] > 0.f) l_run[0] += expf(sv - m_run[0]);
+    if (l_run[1] > 0.f) l_run[1] += expf(sv - m_run[1]);
   }
   const float inv_a = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f;
   const float inv_b = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
@@ -229,7 +241,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 template <int HD>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
                    const int* cu_seqlens, const int* positions, void* out, int n_seqs, int max_new, int nh, int nkv,
-                   int page_size, int chunk, int window, float scale, int skip_single, int sink, cudaStream_t stream) {
+                   int page_size, int chunk, int window, float scale, int skip_single, int sink, float softcap,
+                   const float* slopes, const float* sink_values, cudaStream_t stream) {
   constexpr int STRIDE = HD + 8;
   const size_t smem = (size_t)(BQ * STRIDE + 4 * TILE * STRIDE) * sizeof(__nv_bfloat16);
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -237,7 +250,8 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
   dim3 grid((max_new + BQ - 1) / BQ, nh, n_seqs);
   attn_prefill_kernel<HD><<<grid, NWARPS * 32, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_stride,
-      cu_seqlens, positions, (__nv_bfloat16*)out, nh, nkv, page_size, chunk, window, scale, skip_single, sink);
+      cu_seqlens, positions, (__nv_bfloat16*)out, nh, nkv, page_size, chunk, window, scale, skip_single, sink, softcap,
+      slopes, sink_values);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }
@@ -247,10 +261,11 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
 // bfloat16, head_dim 64, 128 or 192. `cu_seqlens` [n_seqs + 1] are the first flat rows of the requests'
 // new tokens, whose positions are consecutive; `max_new` is the longest run. Other shapes:
 // HB_ERR_UNSUPPORTED (the caller uses the general kernel).
-extern "C" int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+extern "C" int hb_attention_prefill_reshaped(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                     int table_stride, const int* cu_seqlens, const int* positions, void* out,
                                     int n_seqs, int max_new, int nh, int nkv, int hd, int page_size, int chunk,
-                                    int window, float scale, int skip_single, int sink, cudaStream_t stream) {
+                                    int window, float scale, int skip_single, int sink, float softcap,
+                                             const float* slopes, const float* sink_values, cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !cu_seqlens || !positions || !out) return HB_ERR_BAD_ARG;
   if (n_seqs < 0 || max_new < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || table_stride <= 0 ||
       chunk < 0 || window < 0)
@@ -259,12 +274,21 @@ extern "C" int hb_attention_prefill(const void* q, const void* k_pages, const vo
   if (n_seqs == 0 || max_new == 0) return HB_OK;
   if (hd == 192)
     return launch_prefill<192>(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_seqs,
-                               max_new, nh, nkv, page_size, chunk, window, scale, skip_single, sink, stream);
+                               max_new, nh, nkv, page_size, chunk, window, scale, skip_single, sink, softcap, slopes, sink_values, stream);
   if (hd == 128)
     return launch_prefill<128>(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_seqs,
-                               max_new, nh, nkv, page_size, chunk, window, scale, skip_single, sink, stream);
+                               max_new, nh, nkv, page_size, chunk, window, scale, skip_single, sink, softcap, slopes, sink_values, stream);
   if (hd == 64)
     return launch_prefill<64>(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_seqs,
-                              max_new, nh, nkv, page_size, chunk, window, scale, skip_single, sink, stream);
+                              max_new, nh, nkv, page_size, chunk, window, scale, skip_single, sink, softcap, slopes, sink_values, stream);
   return HB_ERR_UNSUPPORTED;
+}
+
+extern "C" int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                    int table_stride, const int* cu_seqlens, const int* positions, void* out,
+                                    int n_seqs, int max_new, int nh, int nkv, int hd, int page_size, int chunk,
+                                    int window, float scale, int skip_single, int sink, cudaStream_t stream) {
+  return hb_attention_prefill_reshaped(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_seqs,
+                                       max_new, nh, nkv, hd, page_size, chunk, window, scale, skip_single, sink, 0.f, nullptr,
+                                       nullptr, stream);
 }

@@ -32,6 +32,7 @@ _SIGNATURES = {
     "hb_attention_decode_tma": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
     "hb_attention_decode_fused": [P, P, I, I, I, F, I, F, F, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P, P, I, F, I, P],
     "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
+    "hb_attention_prefill_reshaped": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, F, P, P, P],
     "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P, I, P, P, P, P],
     "hb_attention_prefill_tc_reshaped": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, F, P, P, I, P, P, P,
                                          P],
@@ -1281,11 +1282,13 @@ def prefill_attention_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int
 def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                       cu_seqlens: torch.Tensor, positions: torch.Tensor, n_seqs: int, max_new: int, chunk: int,
                       window: int, scale: float, skip_single: bool = False,
-                      out: Optional[torch.Tensor] = None, sink: bool = False) -> torch.Tensor:
+                      out: Optional[torch.Tensor] = None, sink: bool = False, softcap: float = 0.0,
+                      slopes: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention for portions of prompts: request ``s`` owns rows ``cu_seqlens[s]..cu_seqlens[s+1]``
     of ``q`` [N, nh, hd], at consecutive positions; bfloat16, flash attention on tensor cores.
     ``skip_single`` leaves the rows of requests that bring one token unwritten (the caller runs
-    the decode kernel for them and passes the same ``out``)."""
+    the decode kernel for them and passes the same ``out``). ``softcap``, ``slopes``, ``sink_values``: as
+    :func:`paged_attention`."""
     _need(q, "q", torch.bfloat16); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
     for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (positions, "positions")):
         _need(t, nm, torch.int32)
@@ -1299,10 +1302,16 @@ def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         raise KernelError("cu_seqlens / block_table do not match the number of requests")
     if out is None:
         out = torch.empty_like(q)
-    _check(lib().hb_attention_prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
-                                      _ptr(cu_seqlens), _ptr(positions), _ptr(out), n_seqs, int(max_new), nh, nkv, hd,
-                                      page_size, int(chunk), int(window), float(scale), int(skip_single), int(sink),
-                                      _stream()),
+    for t, nm in ((slopes, "slopes"), (sink_values, "sink_values")):
+        if t is not None:
+            _need(t, nm, torch.float32)
+            if t.numel() != nh:
+                raise KernelError(f"{nm} needs one number per query head")
+    _check(lib().hb_attention_prefill_reshaped(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                                               block_table.shape[1], _ptr(cu_seqlens), _ptr(positions), _ptr(out), n_seqs,
+                                               int(max_new), nh, nkv, hd, page_size, int(chunk), int(window), float(scale),
+                                               int(skip_single), int(bool(sink) or sink_values is not None),
+                                               float(softcap), _ptr(slopes), _ptr(sink_values), _stream()),
            "attention_prefill")
     return out
 

@@ -40,7 +40,6 @@ def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, 
     (float32 [nh]): of the head's own score instead. ``softcap`` > 0: scores become softcap tanh(score / softcap);
     ``slopes`` (float32 [nh]): slopes[head] * (distance to the key) is taken off after the cap."""
     positions = ctx.positions
-    reshaped = bool(softcap) or slopes is not None or sink_values is not None
     # the decode kernel packs the query heads of one kv head into a 16-row tile; more heads on ONE shared kv
     # head go through it sixteen at a time
     per_call = nh if nkv > 1 or nh <= 16 else 16
@@ -62,10 +61,9 @@ def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, 
     if ctx.max_new == 1 and decode_ok:
         # every token of the step is one request's decoded token: the tensor-core kernel
         return decode(q, ctx.seq_of_token, positions, ctx.max_context)
-    # at least a tile of new tokens somewhere: the tcgen05 kernel; short portions: mma.sync, which takes no reshaped
-    # scores (a cap, a distance bias, a sink with a score of its own): those go to the general kernel below
+    # at least a tile of new tokens somewhere: the tcgen05 kernel; short portions: mma.sync
     tc = ctx.max_new >= ops.PREFILL_TC_MIN_TOKENS and ops.prefill_attention_tc_supported(q.dtype, nh, nkv, hd, ctx.page_size)
-    if ctx.max_new > 1 and ops.prefill_attention_supported(q.dtype, nh, nkv, hd) and (tc or not reshaped):
+    if ctx.max_new > 1 and ops.prefill_attention_supported(q.dtype, nh, nkv, hd):
         # portions of prompts (single tokens of other requests ride along as one-row tiles)
         single = ctx.decode_rows is not None and decode_ok
         if tc:
@@ -75,7 +73,8 @@ def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, 
                                          softcap=softcap, slopes=slopes, sink_values=sink_values)
         else:
             o = ops.prefill_attention(q, k_pages, v_pages, block_table, ctx.cu_seqlens, positions,
-                                      ctx.n_seqs, ctx.max_new, chunk, sliding, scale, skip_single=single, sink=sink)
+                                      ctx.n_seqs, ctx.max_new, chunk, sliding, scale, skip_single=single, sink=sink,
+                                      softcap=softcap, slopes=slopes, sink_values=sink_values)
         if single:
             # single tokens beside portions: their long key ranges go through the split decode kernel
             rows = ctx.decode_rows

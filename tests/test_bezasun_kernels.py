@@ -230,10 +230,11 @@ def test_reshaped_scores_single_tokens(dt, hd, window, tol, cap, bias, sink):
 
 
 @pytest.mark.parametrize("cap,bias,sink", SHAPES)
-@pytest.mark.parametrize("hd,window,new,start", [(64, 0, 300, 0), (128, 0, 260, 40), (64, 70, 130, 62), (64, 0, 140, 700), (128, 200, 129, 199)])
+@pytest.mark.parametrize("hd,window,new,start", [(64, 0, 300, 0), (128, 0, 260, 40), (64, 70, 130, 62), (64, 0, 140, 700), (128, 200, 129, 199),
+                                                 (64, 0, 9, 210), (128, 50, 2, 199)])
 def test_reshaped_scores_portions_on_tcgen05(hd, window, new, start, cap, bias, sink):
-    """Portions of 128 tokens and more through the tcgen05 kernel, with and without key splits, beside the general
-    kernel in float32; all against the plain statement."""
+    """Portions through the mma.sync kernel and, from 128 new tokens, the tcgen05 kernel with and without key splits,
+    beside the general kernel in float32; all against the plain statement."""
     from hi_b200.kernels import ops
 
     nh, nkv, page = 4, 2, 64
@@ -253,13 +254,14 @@ def test_reshaped_scores_portions_on_tcgen05(hd, window, new, start, cap, bias, 
     table, cu = pages.view(1, -1).contiguous(), torch.tensor([0, new], dtype=torch.int32)
     kw = {"softcap": softcap, "slopes": None if slopes is None else dev(slopes), "sink_values": None if sinks is None else dev(sinks)}
     common = (dev(table), dev(cu), dev(pos), 1, new, 0, window, scale)
-    for splits in (1, 3):
+    assert rel(ops.prefill_attention(dev(q, bf), dev(kp, bf), dev(vp, bf), *common, **kw), want) <= 1.5e-2
+    for splits in (1, 3) if new >= ops.PREFILL_TC_MIN_TOKENS else ():
         got = ops.prefill_attention_tc(dev(q, bf), dev(kp, bf), dev(vp, bf), *common, key_splits=splits, **kw)
         torch.cuda.synchronize()
         ops.check_tc_status()
         assert rel(got, want) <= 1.5e-2, splits
     if cap or bias:         # among hundreds of keys a sink's share alone is small
-        assert rel(ops.prefill_attention_tc(dev(q, bf), dev(kp, bf), dev(vp, bf), *common), want) > 0.1
+        assert rel(ops.prefill_attention(dev(q, bf), dev(kp, bf), dev(vp, bf), *common), want) > 0.1
     got = ops.paged_attention(dev(q), dev(kp), dev(vp), dev(table), dev(torch.zeros(new, dtype=torch.int32)), dev(pos), 0, window,
                               scale, t, **kw)
     assert rel(got, want) <= 3e-6
